@@ -140,6 +140,17 @@ const void *mrs_st_tensor_data(void *file, int64_t i);
 int64_t mrs_st_n_metadata(void *file);
 int64_t mrs_st_metadata(void *file, int64_t i, char *key, int64_t key_cap, char *val, int64_t val_cap);
 
+/* ---- recurrent-state slots: one constant-size state per live request (linear attention, state-space layers,
+ *      carried convolution inputs).  acquire: the request's slot (a new one, lowest free first, for an unknown
+ *      request) or -1 when all are taken. ---- */
+void *mrs_state_slots_new(int64_t n_slots);
+void mrs_state_slots_free(void *pool);
+int64_t mrs_state_slots_capacity(void *pool);
+int64_t mrs_state_slots_num_free(void *pool);
+int64_t mrs_state_slots_acquire(void *pool, uint64_t request_id);
+int64_t mrs_state_slots_slot_of(void *pool, uint64_t request_id);
+int32_t mrs_state_slots_release(void *pool, uint64_t request_id);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,120 @@
+/* mrs_b200_seq.h — C ABI of the sequence-mixer kernels (libmrs_b200_seq.so): multi-stream residuals
+ * (hyper-connections), gated linear recurrences with a per-sequence f32 state (linear attention with decay,
+ * selective state spaces), short causal convolutions, windowed attention over a paged cache with unequal key
+ * and value head sizes, grouped-limited expert routing and the expert feed-forward.
+ *
+ * Conventions: raw device pointers, caller-owned memory, stream-ordered, no allocation and no host
+ * synchronisation; every function returns 0 or a cudaError (negative: a bad argument).  `dtype` is the storage
+ * type of activations and of the paged cache (MRS_SEQ_BF16 / MRS_SEQ_F32); residual streams, states, norm
+ * weights and every per-head constant are f32.
+ *
+ * A step's batch is a flat run of `n_tok` tokens from `n_seq` sequences: cu_tok[n_seq + 1] are the token
+ * offsets, past[s] the tokens that sequence s already has in the cache / state, slot[s] its state slot.  A
+ * sequence with past == 0 starts from a zero state whatever its slot holds. */
+#ifndef MRS_B200_SEQ_H
+#define MRS_B200_SEQ_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MRS_SEQ_BF16 = 1, MRS_SEQ_F32 = 2 };
+enum { MRS_SEQ_ACT_NONE = 0, MRS_SEQ_ACT_SILU = 1, MRS_SEQ_ACT_GELU_TANH = 2, MRS_SEQ_ACT_SIGMOID = 3 };
+
+/* ---- residual streams ------------------------------------------------------------------------------ */
+/* streams[t][s][:] = table[ids[t]][:] for every stream s (streams f32 [n_tok, n_streams, width]). */
+int mrs_seq_embed_streams(const void *table, int dtype, const int32_t *ids, float *streams, int n_tok, int n_streams,
+                          int width, int64_t stream);
+/* out[r] = rms_norm(sum_s w_in[s] * streams[row(r)][s]) * (unit_offset + norm_w); rows: token of each output row
+ * (NULL: all tokens in order).  w_in NULL: plain sum of the streams. */
+int mrs_seq_streams_read_norm(const float *streams, const float *w_in, const float *norm_w, float eps, float unit_offset,
+                              const int32_t *rows, void *out, int dtype, int n_rows, int n_streams, int width,
+                              int64_t stream);
+/* streams[t][r] <- sum_s w_mix[s][r] * streams[t][s] + w_out[r] * y[t], all r from the old values; when next_out is
+ * given, the next sublayer's read + norm (as above, with next_in / next_norm_w) runs in the same pass. */
+int mrs_seq_streams_write(float *streams, const float *w_mix, const float *w_out, const void *y, int dtype, int n_tok,
+                          int n_streams, int width, const float *next_in, const float *next_norm_w, float eps,
+                          float unit_offset, void *next_out, int64_t stream);
+
+/* ---- elementwise / norms --------------------------------------------------------------------------- */
+/* out[t][c] = act(x[t][c]) * x[t][half + c]   (x [n_tok, 2 * half]) */
+int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok, int half, int act, int64_t stream);
+/* Root-mean-square norm of f32 rows in `groups` equal parts, times weight, with a gate read from an activation
+ * tensor (row stride gate_ld): gate_first != 0: norm(x * act(gate)) * w; else norm(x) * w * act(gate).  The result,
+ * times out_scale, goes to out[t * out_ld + c]. */
+int mrs_seq_gated_group_norm(const float *x, const void *gate, int64_t gate_ld, const float *weight, void *out, int64_t out_ld,
+                             float out_scale, int dtype, int n_tok, int cols, int groups, float eps, int gate_act,
+                             int gate_first, int64_t stream);
+
+/* ---- short causal convolution + step sizes ---------------------------------------------------------- */
+/* Per channel c < channels: y[t][c] = act(bias[c] + sum_j taps[c][j] * x[t - (n_taps-1) + j][c]) over the tokens of
+ * one sequence; inputs before the portion come from conv_state[slot][n_taps-1][channels] (zeros when past == 0),
+ * which is then advanced to the last n_taps-1 inputs.  x is read from in[t * in_ld + col0 + c]. */
+int mrs_seq_causal_conv(const void *in, int64_t in_ld, int col0, int dtype, const float *taps, const float *bias, int channels,
+                        int n_taps, int act, float *conv_state, const int32_t *cu_tok, const int32_t *past,
+                        const int32_t *slot, const int32_t *seq_of_tok, int n_seq, int n_tok, void *out, int64_t stream);
+/* step[t][h] = softplus(raw[t][h] + bias[h]); decay[t][h] = exp(-exp(a_log[h]) * step[t][h]);  raw at
+ * in[t * in_ld + col0 + h]. */
+int mrs_seq_ssm_steps(const void *in, int64_t in_ld, int col0, int dtype, const float *bias, const float *a_log, int heads,
+                      int n_tok, float *step, float *decay, int64_t stream);
+
+/* ---- gated linear recurrence ---------------------------------------------------------------------- */
+/* Per head h (keys / queries shared by heads / qk_groups neighbouring heads):
+ *   S_t = a_t S_(t-1) + b_t k_t v_t^T     (S f32 [dk, dv], kept in state[slot][h])
+ *   o_t = S_t^T q_t + skip[h] v_t         (o f32 [n_tok, heads * dv])
+ * a_t = decay_tok[t][h] (or decay_head[h] when decay_tok is NULL), b_t = scale_tok[t][h] (1 when NULL), skip NULL: 0.
+ * q, k: [n_tok, qk_groups, dk] with row strides q_ld / k_ld; v: [n_tok, heads, dv] with row stride v_ld; `act` is
+ * applied to q, k and v as they are read. */
+typedef struct {
+  const void *q, *k, *v;
+  int64_t q_ld, k_ld, v_ld;
+  int dtype, act;
+  int heads, qk_groups, dk, dv;
+  const float *decay_tok, *decay_head, *scale_tok, *skip;
+  float *state;
+  const int32_t *cu_tok, *past, *slot;
+  int n_seq, n_tok;
+  float *out;
+} mrs_seq_scan_args;
+int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream);
+
+/* ---- windowed attention over a paged cache --------------------------------------------------------- */
+/* Per-head RMS norm of q (in place) and k with weights shared by the heads (NULL: no norm), then k and v of the new
+ * tokens go to their cache slots.  Cache: k_cache [n_slots, kv_heads, dk], v_cache [n_slots, kv_heads, dv]
+ * (slot = page * page_size + offset), storage type `dtype`. */
+int mrs_seq_qk_norm_store(void *q, int64_t q_ld, const void *k, int64_t k_ld, const void *v, int64_t v_ld, int dtype,
+                          const float *q_norm_w, const float *k_norm_w, float eps, int heads, int kv_heads, int dk, int dv,
+                          void *k_cache, void *v_cache, const int64_t *slot_of_tok, int n_tok, int64_t stream);
+/* out[t][h] = softmax_j(scale * q_t . k_j) v_j over the cached positions j of t's sequence with
+ * 0 <= pos(t) - j < window (window <= 0: every earlier position), times out_scale.  pages [n_seq, pages_ld]. */
+int mrs_seq_window_attention(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, int dtype, int heads,
+                             int kv_heads, int dk, int dv, float scale, int window, const int32_t *pages, int pages_ld,
+                             int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, int n_tok, void *out,
+                             int64_t out_ld, float out_scale, int64_t stream);
+
+/* ---- mixture of experts ---------------------------------------------------------------------------- */
+/* scores = softmax(logits) over n_experts; choice = scores + correction (NULL: 0); experts form n_groups equal
+ * groups of neighbours, a group's score is its largest choice, only the keep_groups best groups stay eligible; the
+ * `top` eligible experts with the largest choice are taken, their weights are their scores (renormalised to sum 1
+ * when renorm != 0).  experts / weights: [n_tok, top]. */
+int mrs_seq_moe_route(const float *logits, const float *correction, int n_tok, int n_experts, int n_groups, int keep_groups,
+                      int top, int renorm, int32_t *experts, float *weights, int64_t stream);
+/* Small batches: hidden[t][k][:] = act(gate_up[e][0:ff] x_t) * (gate_up[e][ff:2ff] x_t), e = experts[t][k]
+ * (gate_up [n_experts, 2 * ff, width]), then out[t] = sum_k weights[t][k] * down[e] hidden[t][k]
+ * (down [n_experts, width, ff]). */
+int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype, const int32_t *experts, int n_tok, int top, int width,
+                        int ff, int act, void *hidden, int64_t stream);
+int mrs_seq_moe_down(const void *hidden, const void *down, int dtype, const int32_t *experts, const float *weights, int n_tok,
+                     int top, int width, int ff, void *out, int64_t stream);
+/* Large batches: rows sorted by expert.  counts[e] rows per expert, order[i] = the (token, k) pair (as token * top + k) at
+ * sorted row i; gather copies x rows into sorted order, combine sums the experts' outputs back per token in k order. */
+int mrs_seq_moe_sort(const int32_t *experts, int n_pairs, int n_experts, int32_t *counts, int32_t *order, int64_t stream);
+int mrs_seq_moe_gather(const void *x, int dtype, const int32_t *order, int n_pairs, int top, int width, void *sorted,
+                       int64_t stream);
+int mrs_seq_moe_combine(const void *sorted_y, int dtype, const int32_t *order, const float *weights, int n_tok, int top,
+                        int width, int32_t *scratch_inverse, void *out, int64_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

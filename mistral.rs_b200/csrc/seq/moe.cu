@@ -1,0 +1,259 @@
+// moe.cu — mixture of experts: the routing rule (softmax scores, a choice bias that does not enter the weights,
+// selection limited to the best groups of neighbouring experts), the expert feed-forward for small batches as two
+// weight-streaming kernels, and the sort / gather / combine steps around per-expert matrix products for large ones.
+#include "seq_common.cuh"
+
+namespace seq {
+
+constexpr int ROUTE_MAX_EXPERTS = 1024;
+
+// one warp per token; scores and choices of all experts in shared memory
+__global__ void moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ correction, int n_tok, int n_experts,
+                                 int n_groups, int keep_groups, int top, int renorm, int32_t *__restrict__ experts,
+                                 float *__restrict__ weights) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int t = blockIdx.x * nw + wib;
+  if (t >= n_tok) return;
+  float *score = sm + (size_t)wib * (2 * n_experts + n_groups), *choice = score + n_experts, *gscore = choice + n_experts;
+  const float *z = logits + (int64_t)t * n_experts;
+  float mx = -INFINITY;
+  for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.0f;
+  for (int e = lane; e < n_experts; e += 32) {
+    const float p = expf(z[e] - mx);
+    score[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+  for (int e = lane; e < n_experts; e += 32) {
+    const float s = score[e] * inv;
+    score[e] = s;
+    choice[e] = s + (correction ? correction[e] : 0.0f);
+  }
+  __syncwarp();
+  const int per = n_experts / n_groups;
+  if (keep_groups < n_groups) {
+    for (int gi = lane; gi < n_groups; gi += 32) {
+      float best = -INFINITY;
+      for (int e = gi * per; e < (gi + 1) * per; e++) best = fmaxf(best, choice[e]);
+      gscore[gi] = best;
+    }
+    __syncwarp();
+    // take the keep_groups best groups one by one (ties: the lower index); a taken group is marked with +inf
+    for (int r = 0; r < keep_groups; r++) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int gi = lane; gi < n_groups; gi += 32) {
+        const float v = gscore[gi];
+        if (v != INFINITY && (v > bv || (v == bv && gi < bi))) { bv = v; bi = gi; }
+      }
+      for (int m = 16; m > 0; m >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (lane == 0 && bi < n_groups) gscore[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < n_experts; e += 32)
+      if (gscore[e / per] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  float wsum = 0.0f;
+  for (int r = 0; r < top; r++) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float v = choice[e];
+      if (!(v != v) && (v > bv || (v == bv && e < bi)) && v != -INFINITY) { bv = v; bi = e; }
+    }
+    for (int m = 16; m > 0; m >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    if (bi == 0x7fffffff) bi = 0;   // fewer eligible experts than `top`: weight 0
+    const float wv = bv == -INFINITY ? 0.0f : score[bi];
+    if (lane == 0) {
+      experts[(int64_t)t * top + r] = bi;
+      weights[(int64_t)t * top + r] = wv;
+      if (bv != -INFINITY) choice[bi] = -INFINITY;
+    }
+    wsum += wv;
+    __syncwarp();
+  }
+  if (renorm && lane == 0 && wsum > 0.0f)
+    for (int r = 0; r < top; r++) weights[(int64_t)t * top + r] /= wsum;
+}
+
+// hidden[t][k][r] = act(gate_up[e][r] . x_t) * (gate_up[e][ff + r] . x_t): one warp per output element;
+// blockIdx.y is the (token, k) pair, pairs laid out [token][k]
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gate_up_kernel(const T *__restrict__ x, const T *__restrict__ gate_up,
+                                                          const int32_t *__restrict__ experts, int top, int width, int ff, int act,
+                                                          T *__restrict__ hidden) {
+  extern __shared__ float xs[];   // [width]
+  const int pair = blockIdx.y, tok = pair / top;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int e = experts[pair];
+  for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32<T>(x[(int64_t)tok * width + c]);
+  __syncthreads();
+  const T *w = gate_up + (int64_t)e * 2 * ff * width;
+  for (int r = blockIdx.x * nw + wib; r < ff; r += gridDim.x * nw) {
+    const T *wg = w + (int64_t)r * width, *wu = w + (int64_t)(ff + r) * width;
+    float ag = 0.0f, au = 0.0f;
+    for (int c = lane; c < width; c += 32) {
+      const float xv = xs[c];
+      ag = fmaf(to_f32<T>(wg[c]), xv, ag);
+      au = fmaf(to_f32<T>(wu[c]), xv, au);
+    }
+    ag = warp_sum(ag);
+    au = warp_sum(au);
+    if (lane == 0) {
+      // the products leave the "matrix product" in the activation type, as the large-batch path's do
+      const float gt = to_f32<T>(from_f32<T>(ag)), up = to_f32<T>(from_f32<T>(au));
+      hidden[(int64_t)pair * ff + r] = from_f32<T>(apply_act(gt, act) * up);
+    }
+  }
+}
+
+// out[t][r] = sum_k weights[t][k] * (down[e_k][r] . hidden[t][k])
+template <typename T>
+__global__ void __launch_bounds__(256) moe_down_kernel(const T *__restrict__ hidden, const T *__restrict__ down,
+                                                       const int32_t *__restrict__ experts, const float *__restrict__ weights, int top,
+                                                       int width, int ff, T *__restrict__ out) {
+  extern __shared__ float hs[];   // [top][ff]
+  const int t = blockIdx.y, lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int c = threadIdx.x; c < top * ff; c += blockDim.x) hs[c] = to_f32<T>(hidden[(int64_t)t * top * ff + c]);
+  __syncthreads();
+  for (int r = blockIdx.x * nw + wib; r < width; r += gridDim.x * nw) {
+    float acc = 0.0f;
+    for (int k = 0; k < top; k++) {
+      const T *wd = down + ((int64_t)experts[(int64_t)t * top + k] * width + r) * ff;
+      float a = 0.0f;
+      for (int c = lane; c < ff; c += 32) a = fmaf(to_f32<T>(wd[c]), hs[k * ff + c], a);
+      a = warp_sum(a);
+      acc = fmaf(weights[(int64_t)t * top + k], to_f32<T>(from_f32<T>(a)), acc);
+    }
+    if (lane == 0) out[(int64_t)t * width + r] = from_f32<T>(acc);
+  }
+}
+
+// ---- sorted path --------------------------------------------------------------------------------------------------
+// single CTA: counts per expert, then every (token, k) pair takes the next free row of its expert's range
+__global__ void moe_sort_kernel(const int32_t *__restrict__ experts, int n_pairs, int n_experts, int32_t *__restrict__ counts,
+                                int32_t *__restrict__ order) {
+  extern __shared__ int32_t cnt[];   // [n_experts] counts, then [n_experts] running offsets
+  int32_t *off = cnt + n_experts;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&cnt[experts[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < n_experts; e++) {
+      off[e] = run;
+      run += cnt[e];
+      counts[e] = cnt[e];
+    }
+  }
+  __syncthreads();
+  // rows of one expert may land in any order: each row's product does not depend on its place
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) order[atomicAdd(&off[experts[i]], 1)] = i;
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T *__restrict__ x, const int32_t *__restrict__ order, int top, int width, T *__restrict__ sorted) {
+  const int i = blockIdx.x, t = order[i] / top;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) sorted[(int64_t)i * width + c] = x[(int64_t)t * width + c];
+}
+
+__global__ void moe_inverse_kernel(const int32_t *__restrict__ order, int n_pairs, int32_t *__restrict__ inverse) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_pairs) inverse[order[i]] = i;
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T *__restrict__ sorted_y, const int32_t *__restrict__ inverse, const float *__restrict__ weights,
+                                   int top, int width, T *__restrict__ out) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < top; k++)
+      acc = fmaf(weights[(int64_t)t * top + k], to_f32<T>(sorted_y[(int64_t)inverse[(int64_t)t * top + k] * width + c]), acc);
+    out[(int64_t)t * width + c] = from_f32<T>(acc);
+  }
+}
+
+}  // namespace seq
+
+using namespace seq;
+
+extern "C" int mrs_seq_moe_route(const float *logits, const float *correction, int n_tok, int n_experts, int n_groups, int keep_groups,
+                                 int top, int renorm, int32_t *experts, float *weights, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (n_experts < 1 || n_experts > ROUTE_MAX_EXPERTS || n_groups < 1 || n_experts % n_groups || keep_groups < 1 ||
+      keep_groups > n_groups || top < 1 || top > n_experts)
+    return -2;
+  const int warps = 4;
+  const size_t bytes = (size_t)warps * (2 * n_experts + n_groups) * sizeof(float);
+  moe_route_kernel<<<(n_tok + warps - 1) / warps, warps * 32, bytes, (cudaStream_t)stream>>>(
+      logits, correction, n_tok, n_experts, n_groups, keep_groups, top, renorm, experts, weights);
+  return launch_status();
+}
+
+extern "C" int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype, const int32_t *experts, int n_tok, int top, int width,
+                                   int ff, int act, void *hidden, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if ((size_t)width * sizeof(float) > 160 * 1024) return -2;
+  const int warps = 8, bx = (ff + warps - 1) / warps;
+  const size_t bytes = (size_t)width * sizeof(float);
+  SEQ_DISPATCH_DTYPE(dtype, {
+    auto kern = moe_gate_up_kernel<T>;
+    if (bytes > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    kern<<<dim3(bx < 64 ? bx : 64, n_tok * top), warps * 32, bytes, (cudaStream_t)stream>>>(
+        (const T *)x, (const T *)gate_up, experts, top, width, ff, act, (T *)hidden);
+  });
+  return launch_status();
+}
+
+extern "C" int mrs_seq_moe_down(const void *hidden, const void *down, int dtype, const int32_t *experts, const float *weights, int n_tok,
+                                int top, int width, int ff, void *out, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  const size_t bytes = (size_t)top * ff * sizeof(float);
+  if (bytes > 160 * 1024) return -2;
+  const int warps = 8, bx = (width + warps - 1) / warps;
+  SEQ_DISPATCH_DTYPE(dtype, {
+    auto kern = moe_down_kernel<T>;
+    if (bytes > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    kern<<<dim3(bx < 64 ? bx : 64, n_tok), warps * 32, bytes, (cudaStream_t)stream>>>(
+        (const T *)hidden, (const T *)down, experts, weights, top, width, ff, (T *)out);
+  });
+  return launch_status();
+}
+
+extern "C" int mrs_seq_moe_sort(const int32_t *experts, int n_pairs, int n_experts, int32_t *counts, int32_t *order, int64_t stream) {
+  if (n_pairs <= 0) return 0;
+  moe_sort_kernel<<<1, 1024, 2 * n_experts * sizeof(int32_t), (cudaStream_t)stream>>>(experts, n_pairs, n_experts, counts, order);
+  return launch_status();
+}
+
+extern "C" int mrs_seq_moe_gather(const void *x, int dtype, const int32_t *order, int n_pairs, int top, int width, void *sorted,
+                                  int64_t stream) {
+  if (n_pairs <= 0) return 0;
+  SEQ_DISPATCH_DTYPE(dtype, (moe_gather_kernel<T><<<n_pairs, 128, 0, (cudaStream_t)stream>>>((const T *)x, order, top, width, (T *)sorted)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_moe_combine(const void *sorted_y, int dtype, const int32_t *order, const float *weights, int n_tok, int top,
+                                   int width, int32_t *scratch_inverse, void *out, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  const int n_pairs = n_tok * top;
+  moe_inverse_kernel<<<(n_pairs + 255) / 256, 256, 0, (cudaStream_t)stream>>>(order, n_pairs, scratch_inverse);
+  SEQ_DISPATCH_DTYPE(dtype, (moe_combine_kernel<T><<<n_tok, 128, 0, (cudaStream_t)stream>>>((const T *)sorted_y, scratch_inverse, weights,
+                                                                                          top, width, (T *)out)));
+  return launch_status();
+}

@@ -1,0 +1,284 @@
+// scan.cu — gated linear recurrences with an f32 state per (sequence, head), and what surrounds them: the short
+// causal convolution with its carried inputs, the step-size / decay preparation of a selective state space, the
+// gated group RMS norm of the recurrence's output, and the split GLU.
+//
+//   S_t = a_t S_(t-1) + b_t k_t v_t^T ,  o_t = S_t^T q_t + skip v_t
+//
+// covers linear attention with a fixed per-head decay (a_t constant, b_t = 1, silu on q / k / v) and the state-space
+// form (k = B, q = C, v = x, a_t = exp(-exp(A_log) dt_t), b_t = dt_t, skip = D).  The same kernel runs a prompt
+// portion and a single decoded token: the state is read from the sequence's slot (or taken as zero when the
+// sequence starts), advanced token by token in registers, and written back.
+#include "seq_common.cuh"
+
+namespace seq {
+
+// One CTA: one sequence, one head, CW state columns.  Thread (col, part) keeps rows [part * RK, part * RK + RK) of its
+// column in registers; the `parts` partitions of a column sit in neighbouring lanes, so the dot with q ends in a few
+// shuffles.  q / k / v / a / b of TC tokens are staged in shared memory per round.
+template <typename T, int RK, int TC>
+__global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw) {
+  extern __shared__ __align__(16) float smem[];
+  const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cw;
+  const int t0 = a.cu_tok[b], t1 = a.cu_tok[b + 1];
+  if (t1 <= t0) return;
+  const int dk = a.dk, dv = a.dv, heads = a.heads;
+  const int g = h / (heads / a.qk_groups);
+  const int part = threadIdx.x % parts, cl = threadIdx.x / parts;
+  const int PS = RK + 4;                 // padded partition stride (floats): 16-byte aligned, conflict-free
+  const int dks = parts * PS;
+  float *qs = smem, *ks = qs + TC * dks, *vs = ks + TC * dks, *os = vs + TC * cw, *as = os + TC * cw, *bs = as + TC;
+  float *state = a.state + ((int64_t)a.slot[b] * heads + h) * dk * dv;
+
+  float S[RK];
+  if (a.past[b] > 0) {   // stage the tile [dk, cw] through shared memory so the global reads run along columns
+    float *tile = smem;
+    for (int e = threadIdx.x; e < parts * RK * cw; e += blockDim.x) {
+      const int r = e / cw, c = e % cw;
+      tile[e] = (r < dk && col0 + c < dv) ? state[(int64_t)r * dv + col0 + c] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < RK; r++) S[r] = tile[(part * RK + r) * cw + cl];
+    __syncthreads();
+  } else {
+#pragma unroll
+    for (int r = 0; r < RK; r++) S[r] = 0.0f;
+  }
+  const float skip = a.skip ? a.skip[h] : 0.0f;
+  const T *q = (const T *)a.q, *k = (const T *)a.k, *v = (const T *)a.v;
+
+  for (int c0 = t0; c0 < t1; c0 += TC) {
+    const int n = min(TC, t1 - c0);
+    for (int e = threadIdx.x; e < n * parts * RK; e += blockDim.x) {
+      const int i = e / (parts * RK), d = e % (parts * RK);
+      float qv = 0.0f, kv = 0.0f;
+      if (d < dk) {
+        qv = apply_act(to_f32<T>(q[(int64_t)(c0 + i) * a.q_ld + g * dk + d]), a.act);
+        kv = apply_act(to_f32<T>(k[(int64_t)(c0 + i) * a.k_ld + g * dk + d]), a.act);
+      }
+      const int at = i * dks + (d / RK) * PS + d % RK;
+      qs[at] = qv;
+      ks[at] = kv;
+    }
+    for (int e = threadIdx.x; e < n * cw; e += blockDim.x) {
+      const int i = e / cw, c = e % cw;
+      vs[e] = col0 + c < dv ? apply_act(to_f32<T>(v[(int64_t)(c0 + i) * a.v_ld + h * dv + col0 + c]), a.act) : 0.0f;
+    }
+    if (threadIdx.x < n) {
+      const int64_t th = (int64_t)(c0 + threadIdx.x) * heads + h;
+      as[threadIdx.x] = a.decay_tok ? a.decay_tok[th] : a.decay_head[h];
+      bs[threadIdx.x] = a.scale_tok ? a.scale_tok[th] : 1.0f;
+    }
+    __syncthreads();
+    for (int i = 0; i < n; i++) {
+      const float av = as[i], vv = vs[i * cw + cl], bv = bs[i] * vv;
+      const float4 *kp = (const float4 *)(ks + i * dks + part * PS), *qp = (const float4 *)(qs + i * dks + part * PS);
+      float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+#pragma unroll
+      for (int r = 0; r < RK; r += 4) {
+        const float4 k4 = kp[r / 4], q4 = qp[r / 4];
+        S[r] = fmaf(k4.x, bv, av * S[r]);
+        S[r + 1] = fmaf(k4.y, bv, av * S[r + 1]);
+        S[r + 2] = fmaf(k4.z, bv, av * S[r + 2]);
+        S[r + 3] = fmaf(k4.w, bv, av * S[r + 3]);
+        acc0 = fmaf(S[r], q4.x, acc0);
+        acc1 = fmaf(S[r + 1], q4.y, acc1);
+        acc2 = fmaf(S[r + 2], q4.z, acc2);
+        acc3 = fmaf(S[r + 3], q4.w, acc3);
+      }
+      float acc = (acc0 + acc1) + (acc2 + acc3);
+      for (int m = 1; m < parts; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+      if (part == 0) os[i * cw + cl] = fmaf(skip, vv, acc);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * cw; e += blockDim.x) {
+      const int i = e / cw, c = e % cw;
+      if (col0 + c < dv) a.out[(int64_t)(c0 + i) * heads * dv + h * dv + col0 + c] = os[e];
+    }
+    __syncthreads();
+  }
+  {   // the state goes back the way it came
+    float *tile = smem;
+#pragma unroll
+    for (int r = 0; r < RK; r++) tile[(part * RK + r) * cw + cl] = S[r];
+    __syncthreads();
+    for (int e = threadIdx.x; e < parts * RK * cw; e += blockDim.x) {
+      const int r = e / cw, c = e % cw;
+      if (r < dk && col0 + c < dv) state[(int64_t)r * dv + col0 + c] = tile[e];
+    }
+  }
+}
+
+template <typename T, int RK, int TC>
+static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
+  int parts = 1;
+  while (parts * RK < a.dk) parts <<= 1;
+  if (parts > 32) return -2;
+  const int unit = 32 / parts;                                  // columns per warp
+  int cw = min(256 / parts, (a.dv + unit - 1) / unit * unit);
+  const int dks = parts * (RK + 4);
+  const size_t chunk = (size_t)(2 * TC * dks + 2 * TC * cw + 2 * TC) * sizeof(float);
+  const size_t tile = (size_t)parts * RK * cw * sizeof(float);
+  const size_t bytes = chunk > tile ? chunk : tile;
+  auto kern = linear_scan_kernel<T, RK, TC>;
+  if (bytes > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid((a.dv + cw - 1) / cw, a.heads, a.n_seq);
+  kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw);
+  return launch_status();
+}
+
+// ---- short causal convolution ------------------------------------------------------------------------------------
+// one thread per (token, channel): taps reach back into the portion or, before its start, into the carried inputs
+template <typename T>
+__global__ void causal_conv_kernel(const T *__restrict__ in, int64_t in_ld, int col0, const float *__restrict__ taps,
+                                   const float *__restrict__ bias, int channels, int n_taps, int act,
+                                   const float *__restrict__ conv_state, const int32_t *__restrict__ cu_tok,
+                                   const int32_t *__restrict__ past, const int32_t *__restrict__ slot,
+                                   const int32_t *__restrict__ seq_of_tok, T *__restrict__ out) {
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int s = seq_of_tok[t], first = cu_tok[s], i = t - first, carried = n_taps - 1;
+  const bool has_past = past[s] > 0;
+  const float *st = conv_state + (int64_t)slot[s] * carried * channels;
+  float acc = bias ? bias[c] : 0.0f;
+  for (int j = 0; j < n_taps; j++) {
+    const int src = i - carried + j;   // index inside the portion
+    float x;
+    if (src >= 0) x = to_f32<T>(in[(int64_t)(first + src) * in_ld + col0 + c]);
+    else x = has_past ? st[(int64_t)(carried + src) * channels + c] : 0.0f;
+    acc = fmaf(taps[(int64_t)c * n_taps + j], x, acc);
+  }
+  out[(int64_t)t * channels + c] = from_f32<T>(apply_act(acc, act));
+}
+
+// runs after the convolution: the carried inputs become the last n_taps-1 inputs of the sequence
+template <typename T>
+__global__ void conv_state_advance_kernel(const T *__restrict__ in, int64_t in_ld, int col0, int channels, int n_taps,
+                                          float *__restrict__ conv_state, const int32_t *__restrict__ cu_tok,
+                                          const int32_t *__restrict__ past, const int32_t *__restrict__ slot) {
+  const int s = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int first = cu_tok[s], n = cu_tok[s + 1] - first, carried = n_taps - 1;
+  if (n <= 0) return;
+  const bool has_past = past[s] > 0;
+  float *st = conv_state + (int64_t)slot[s] * carried * channels;
+  for (int j = 0; j < carried; j++) {   // ascending: entry j reads old entry j + n, never one already rewritten
+    const int src = n - carried + j;
+    float x;
+    if (src >= 0) x = to_f32<T>(in[(int64_t)(first + src) * in_ld + col0 + c]);
+    else x = has_past ? st[(int64_t)(carried + src) * channels + c] : 0.0f;
+    st[(int64_t)j * channels + c] = x;
+  }
+}
+
+template <typename T>
+__global__ void ssm_steps_kernel(const T *__restrict__ in, int64_t in_ld, int col0, const float *__restrict__ bias,
+                                 const float *__restrict__ a_log, int heads, int n_tok, float *__restrict__ step,
+                                 float *__restrict__ decay) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_tok * heads) return;
+  const int t = e / heads, h = e % heads;
+  const float dt = softplus_f(to_f32<T>(in[(int64_t)t * in_ld + col0 + h]) + bias[h]);
+  step[e] = dt;
+  decay[e] = expf(-expf(a_log[h]) * dt);
+}
+
+// ---- gated group RMS norm ------------------------------------------------------------------------------------------
+// one CTA per (token, group)
+template <typename T>
+__global__ void gated_group_norm_kernel(const float *__restrict__ x, const T *__restrict__ gate, int64_t gate_ld,
+                                        const float *__restrict__ weight, T *__restrict__ out, int64_t out_ld, float out_scale, int cols,
+                                        int groups, float eps, int gate_act, int gate_first) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, gr = blockIdx.y, n = cols / groups, c0 = gr * n;
+  const float *xr = x + (int64_t)t * cols + c0;
+  const T *gp = gate ? gate + (int64_t)t * gate_ld + c0 : nullptr;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = xr[c];
+    if (gp && gate_first) v *= apply_act(to_f32<T>(gp[c]), gate_act);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf_exact(block_sum(ss, red) / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = xr[c];
+    const float gv = gp ? apply_act(to_f32<T>(gp[c]), gate_act) : 1.0f;
+    if (gate_first) v = v * gv * inv * weight[c0 + c];
+    else v = v * inv * weight[c0 + c] * gv;
+    out[(int64_t)t * out_ld + c0 + c] = from_f32<T>(v * out_scale);
+  }
+}
+
+template <typename T>
+__global__ void glu_split_kernel(const T *__restrict__ x, T *__restrict__ out, int64_t total, int half, int act) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int64_t t = e / half, c = e % half;
+  const float gt = to_f32<T>(x[t * 2 * half + c]), up = to_f32<T>(x[t * 2 * half + half + c]);
+  out[e] = from_f32<T>(apply_act(gt, act) * up);
+}
+
+}  // namespace seq
+
+using namespace seq;
+
+extern "C" int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream) {
+  const mrs_seq_scan_args &a = *args;
+  if (a.n_tok <= 0 || a.n_seq <= 0) return 0;
+  if (a.heads <= 0 || a.qk_groups <= 0 || a.heads % a.qk_groups || a.dk <= 0 || a.dv <= 0) return -2;
+  if (!a.decay_tok && !a.decay_head) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (a.dk <= 128) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 16, 16>(a, st)));
+  if (a.dk <= 512) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 32, 8>(a, st)));
+  return -2;
+}
+
+extern "C" int mrs_seq_causal_conv(const void *in, int64_t in_ld, int col0, int dtype, const float *taps, const float *bias,
+                                   int channels, int n_taps, int act, float *conv_state, const int32_t *cu_tok,
+                                   const int32_t *past, const int32_t *slot, const int32_t *seq_of_tok, int n_seq, int n_tok,
+                                   void *out, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (n_taps < 1 || channels < 1) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int th = 128;
+  SEQ_DISPATCH_DTYPE(dtype, {
+    causal_conv_kernel<T><<<dim3(n_tok, (channels + th - 1) / th), th, 0, st>>>((const T *)in, in_ld, col0, taps, bias, channels,
+                                                                               n_taps, act, conv_state, cu_tok, past, slot,
+                                                                               seq_of_tok, (T *)out);
+    if (n_taps > 1)
+      conv_state_advance_kernel<T><<<dim3((channels + th - 1) / th, n_seq), th, 0, st>>>((const T *)in, in_ld, col0, channels,
+                                                                                        n_taps, conv_state, cu_tok, past, slot);
+  });
+  return launch_status();
+}
+
+extern "C" int mrs_seq_ssm_steps(const void *in, int64_t in_ld, int col0, int dtype, const float *bias, const float *a_log, int heads,
+                                 int n_tok, float *step, float *decay, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  const int total = n_tok * heads;
+  SEQ_DISPATCH_DTYPE(dtype, (ssm_steps_kernel<T><<<(total + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+                                (const T *)in, in_ld, col0, bias, a_log, heads, n_tok, step, decay)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_gated_group_norm(const float *x, const void *gate, int64_t gate_ld, const float *weight, void *out, int64_t out_ld,
+                                        float out_scale, int dtype, int n_tok, int cols, int groups, float eps, int gate_act,
+                                        int gate_first, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (groups < 1 || cols % groups) return -2;
+  const int n = cols / groups, th = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+  SEQ_DISPATCH_DTYPE(dtype, (gated_group_norm_kernel<T><<<dim3(n_tok, groups), th, 0, (cudaStream_t)stream>>>(
+                                x, (const T *)gate, gate_ld, weight, (T *)out, out_ld, out_scale, cols, groups, eps, gate_act, gate_first)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok, int half, int act, int64_t stream) {
+  const int64_t total = (int64_t)n_tok * half;
+  if (total <= 0) return 0;
+  SEQ_DISPATCH_DTYPE(dtype, (glu_split_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                                (const T *)x, (T *)out, total, half, act)));
+  return launch_status();
+}

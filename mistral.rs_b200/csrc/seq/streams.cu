@@ -1,0 +1,134 @@
+// streams.cu — multi-stream residual (hyper-connections): the model keeps `n_streams` f32 copies of the residual per
+// token.  A sublayer reads a weighted sum of them (fused here with its RMS norm) and writes back a mix of the old
+// streams plus its scaled output (fused with the NEXT sublayer's read + norm, the way add + RMSNorm are one kernel in
+// the single-stream decoder).  One CTA per token; the streams never leave f32.
+#include "seq_common.cuh"
+
+namespace seq {
+
+constexpr int MAX_STREAMS = 8;
+
+template <typename T>
+__global__ void embed_streams_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids, float *__restrict__ streams,
+                                     int n_streams, int width) {
+  const int t = blockIdx.x;
+  const T *row = table + (int64_t)ids[t] * width;
+  float *dst = streams + (int64_t)t * n_streams * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_f32<T>(row[c]);
+    for (int s = 0; s < n_streams; s++) dst[(int64_t)s * width + c] = v;
+  }
+}
+
+// u = sum_s w_in[s] x_s ; out = u / sqrt(mean(u^2) + eps) * (unit_offset + w)
+template <typename T>
+__global__ void streams_read_norm_kernel(const float *__restrict__ streams, const float *__restrict__ w_in,
+                                         const float *__restrict__ norm_w, float eps, float unit_offset,
+                                         const int32_t *__restrict__ rows, T *__restrict__ out, int n_streams, int width) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  const float *src = streams + (int64_t)t * n_streams * width;
+  float win[MAX_STREAMS];
+#pragma unroll
+  for (int s = 0; s < MAX_STREAMS; s++) win[s] = s < n_streams ? (w_in ? w_in[s] : 1.0f) : 0.0f;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float u = 0.0f;
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; s++)
+      if (s < n_streams) u = fmaf(win[s], src[(int64_t)s * width + c], u);
+    ss = fmaf(u, u, ss);
+  }
+  const float inv = rsqrtf_exact(block_sum(ss, red) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float u = 0.0f;
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; s++)
+      if (s < n_streams) u = fmaf(win[s], src[(int64_t)s * width + c], u);
+    out[(int64_t)r * width + c] = from_f32<T>(u * inv * (unit_offset + norm_w[c]));
+  }
+}
+
+// x_r <- sum_s mix[s][r] x_s + w_out[r] y, every r from the old x; then (optionally) the next read + norm
+template <typename T>
+__global__ void streams_write_kernel(float *__restrict__ streams, const float *__restrict__ w_mix, const float *__restrict__ w_out,
+                                     const T *__restrict__ y, int n_streams, int width, const float *__restrict__ next_in,
+                                     const float *__restrict__ next_norm_w, float eps, float unit_offset, T *__restrict__ next_out) {
+  __shared__ float red[33];
+  __shared__ float mix[MAX_STREAMS * MAX_STREAMS], wout[MAX_STREAMS], nin[MAX_STREAMS];
+  const int t = blockIdx.x;
+  if (threadIdx.x < n_streams * n_streams) mix[threadIdx.x] = w_mix[threadIdx.x];
+  if (threadIdx.x < n_streams) {
+    wout[threadIdx.x] = w_out[threadIdx.x];
+    nin[threadIdx.x] = next_in ? next_in[threadIdx.x] : 0.0f;
+  }
+  __syncthreads();
+  float *x = streams + (int64_t)t * n_streams * width;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float old[MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; s++)
+      if (s < n_streams) old[s] = x[(int64_t)s * width + c];
+    const float yv = to_f32<T>(y[(int64_t)t * width + c]);
+    float u = 0.0f;
+#pragma unroll
+    for (int r = 0; r < MAX_STREAMS; r++) {
+      if (r < n_streams) {
+        float acc = wout[r] * yv;
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; s++)
+          if (s < n_streams) acc = fmaf(mix[s * n_streams + r], old[s], acc);
+        x[(int64_t)r * width + c] = acc;
+        u = fmaf(nin[r], acc, u);
+      }
+    }
+    ss = fmaf(u, u, ss);
+  }
+  if (next_out == nullptr) return;
+  const float inv = rsqrtf_exact(block_sum(ss, red) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {   // the thread re-reads the columns it wrote itself
+    float u = 0.0f;
+#pragma unroll
+    for (int r = 0; r < MAX_STREAMS; r++)
+      if (r < n_streams) u = fmaf(nin[r], x[(int64_t)r * width + c], u);
+    next_out[(int64_t)t * width + c] = from_f32<T>(u * inv * (unit_offset + next_norm_w[c]));
+  }
+}
+
+static int threads_for(int width) { return width >= 1024 ? 256 : (width >= 256 ? 128 : 64); }
+
+}  // namespace seq
+
+using namespace seq;
+
+extern "C" int mrs_seq_embed_streams(const void *table, int dtype, const int32_t *ids, float *streams, int n_tok, int n_streams,
+                                     int width, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (n_streams < 1 || n_streams > MAX_STREAMS) return -2;
+  SEQ_DISPATCH_DTYPE(dtype, (embed_streams_kernel<T><<<n_tok, threads_for(width), 0, (cudaStream_t)stream>>>(
+                                (const T *)table, ids, streams, n_streams, width)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_streams_read_norm(const float *streams, const float *w_in, const float *norm_w, float eps, float unit_offset,
+                                         const int32_t *rows, void *out, int dtype, int n_rows, int n_streams, int width,
+                                         int64_t stream) {
+  if (n_rows <= 0) return 0;
+  if (n_streams < 1 || n_streams > MAX_STREAMS) return -2;
+  SEQ_DISPATCH_DTYPE(dtype, (streams_read_norm_kernel<T><<<n_rows, threads_for(width), 0, (cudaStream_t)stream>>>(
+                                streams, w_in, norm_w, eps, unit_offset, rows, (T *)out, n_streams, width)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_streams_write(float *streams, const float *w_mix, const float *w_out, const void *y, int dtype, int n_tok,
+                                     int n_streams, int width, const float *next_in, const float *next_norm_w, float eps,
+                                     float unit_offset, void *next_out, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (n_streams < 1 || n_streams > MAX_STREAMS) return -2;
+  SEQ_DISPATCH_DTYPE(dtype, (streams_write_kernel<T><<<n_tok, threads_for(width), 0, (cudaStream_t)stream>>>(
+                                streams, w_mix, w_out, (const T *)y, n_streams, width, next_in, next_norm_w, eps, unit_offset,
+                                (T *)next_out)));
+  return launch_status();
+}

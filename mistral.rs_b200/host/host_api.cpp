@@ -5,6 +5,7 @@
 #include "kv_index.hpp"
 #include "safetensors_reader.hpp"
 #include "sampler_tail.hpp"
+#include "state_slots.hpp"
 
 #include <cstring>
 
@@ -348,5 +349,14 @@ int64_t mrs_st_metadata(void *h, int64_t i, char *key, int64_t key_cap, char *va
   copy_out(m[(size_t)i].first, key, key_cap);
   return copy_out(m[(size_t)i].second, val, val_cap);
 }
+
+/* ---- recurrent-state slots ---- */
+void *mrs_state_slots_new(int64_t n_slots) { return n_slots > 0 ? new StateSlotPool((size_t)n_slots) : nullptr; }
+void mrs_state_slots_free(void *p) { delete (StateSlotPool *)p; }
+int64_t mrs_state_slots_capacity(void *p) { return (int64_t)((StateSlotPool *)p)->capacity(); }
+int64_t mrs_state_slots_num_free(void *p) { return (int64_t)((StateSlotPool *)p)->num_free(); }
+int64_t mrs_state_slots_acquire(void *p, uint64_t request_id) { return ((StateSlotPool *)p)->acquire(request_id); }
+int64_t mrs_state_slots_slot_of(void *p, uint64_t request_id) { return ((StateSlotPool *)p)->slot_of(request_id); }
+int32_t mrs_state_slots_release(void *p, uint64_t request_id) { return ((StateSlotPool *)p)->release(request_id) ? 1 : 0; }
 
 }  // extern "C"

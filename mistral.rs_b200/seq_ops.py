@@ -1,0 +1,220 @@
+"""ctypes front-end of libmrs_b200_seq.so (include/mrs_b200_seq.h): residual streams, gated linear recurrences,
+short causal convolutions, windowed attention over a paged cache, expert routing.  PyTorch supplies memory and the
+stream; there is no CPU fallback — a missing library is built on first use (nvcc, sm_100a) or the import fails."""
+import ctypes
+import os
+import subprocess
+
+import torch
+
+from . import ExtensionMissing
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SEQ_LIB_PATH = os.path.join(_HERE, "libmrs_b200_seq.so")
+BF16, F32 = 1, 2
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID = 0, 1, 2, 3
+DTYPE_CODE = {torch.bfloat16: BF16, torch.float32: F32}
+_lib = None
+
+
+def make_target(directory, product):
+    """Build `product` with the Makefile in `directory` when it is missing (a fresh checkout)."""
+    if os.path.exists(product):
+        return
+    try:
+        subprocess.check_call(["make", "-s", "-C", directory], stdout=subprocess.DEVNULL)
+    except (OSError, subprocess.CalledProcessError) as e:
+        raise ExtensionMissing(f"{product} is missing and `make -C {directory}` failed: {e}") from e
+    if not os.path.exists(product):
+        raise ExtensionMissing(f"{product} was not produced by `make -C {directory}`")
+
+
+def ensure_host_lib():
+    from . import kv_index
+    make_target(os.path.join(_HERE, "host"), kv_index.HOST_LIB_PATH)
+    L = kv_index.host_lib()
+    if getattr(L, "_seq_types", None) is None:
+        L.mrs_state_slots_new.restype = ctypes.c_void_p
+        for f in ("capacity", "num_free", "acquire", "slot_of"):
+            getattr(L, f"mrs_state_slots_{f}").restype = ctypes.c_int64
+        L._seq_types = True
+    return L
+
+
+class ScanArgs(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("q_ld", ctypes.c_int64), ("k_ld", ctypes.c_int64), ("v_ld", ctypes.c_int64),
+                ("dtype", ctypes.c_int), ("act", ctypes.c_int),
+                ("heads", ctypes.c_int), ("qk_groups", ctypes.c_int), ("dk", ctypes.c_int), ("dv", ctypes.c_int),
+                ("decay_tok", ctypes.c_void_p), ("decay_head", ctypes.c_void_p), ("scale_tok", ctypes.c_void_p),
+                ("skip", ctypes.c_void_p), ("state", ctypes.c_void_p),
+                ("cu_tok", ctypes.c_void_p), ("past", ctypes.c_void_p), ("slot", ctypes.c_void_p),
+                ("n_seq", ctypes.c_int), ("n_tok", ctypes.c_int), ("out", ctypes.c_void_p)]
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        make_target(os.path.join(_HERE, "csrc", "seq"), SEQ_LIB_PATH)
+        _lib = ctypes.CDLL(SEQ_LIB_PATH)
+    return _lib
+
+
+def _p(t, offset=0):
+    """Device address of element `offset` of a tensor (None -> NULL)."""
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr() + offset * t.element_size())
+
+
+def _st(t):
+    return ctypes.c_int64(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ok(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed: {'bad argument' if rc < 0 else 'cudaError'} {rc}")
+
+
+_i, _f, _l = ctypes.c_int, ctypes.c_float, ctypes.c_int64
+
+
+def embed_streams(table, ids, n_streams):
+    T, W = ids.numel(), table.shape[1]
+    out = torch.empty(T, n_streams, W, dtype=torch.float32, device=table.device)
+    _ok(lib().mrs_seq_embed_streams(_p(table), _i(DTYPE_CODE[table.dtype]), _p(ids), _p(out), _i(T), _i(n_streams), _i(W), _st(table)),
+        "embed_streams")
+    return out
+
+
+def streams_read_norm(streams, w_in, norm_w, eps, unit_offset, dtype, rows=None):
+    T, S, W = streams.shape
+    n = T if rows is None else rows.numel()
+    out = torch.empty(n, W, dtype=dtype, device=streams.device)
+    _ok(lib().mrs_seq_streams_read_norm(_p(streams), _p(w_in), _p(norm_w), _f(eps), _f(unit_offset), _p(rows), _p(out),
+                                        _i(DTYPE_CODE[dtype]), _i(n), _i(S), _i(W), _st(streams)), "streams_read_norm")
+    return out
+
+
+def streams_write(streams, w_mix, w_out, y, next_in=None, next_norm_w=None, eps=0.0, unit_offset=0.0):
+    """In place on `streams`; returns the next sublayer's normed input when next_norm_w is given."""
+    T, S, W = streams.shape
+    nxt = torch.empty(T, W, dtype=y.dtype, device=y.device) if next_norm_w is not None else None
+    _ok(lib().mrs_seq_streams_write(_p(streams), _p(w_mix), _p(w_out), _p(y), _i(DTYPE_CODE[y.dtype]), _i(T), _i(S), _i(W),
+                                    _p(next_in), _p(next_norm_w), _f(eps), _f(unit_offset), _p(nxt), _st(streams)), "streams_write")
+    return nxt
+
+
+def glu_split(x, act):
+    T, two = x.shape
+    out = torch.empty(T, two // 2, dtype=x.dtype, device=x.device)
+    _ok(lib().mrs_seq_glu_split(_p(x), _p(out), _i(DTYPE_CODE[x.dtype]), _i(T), _i(two // 2), _i(act), _st(x)), "glu_split")
+    return out
+
+
+def gated_group_norm(x, gate, gate_col, weight, groups, eps, gate_act, gate_first, out, out_col=0, out_scale=1.0):
+    """x f32 [T, C]; the gate is columns gate_col.. of `gate`; writes columns out_col.. of `out`."""
+    T, C = x.shape
+    _ok(lib().mrs_seq_gated_group_norm(_p(x), _p(gate, gate_col), _l(gate.stride(0)), _p(weight), _p(out, out_col), _l(out.stride(0)),
+                                       _f(out_scale), _i(DTYPE_CODE[out.dtype]), _i(T), _i(C), _i(groups), _f(eps), _i(gate_act),
+                                       _i(int(gate_first)), _st(x)), "gated_group_norm")
+
+
+def causal_conv(inp, col0, channels, taps, bias, act, conv_state, batch):
+    T = inp.shape[0]
+    out = torch.empty(T, channels, dtype=inp.dtype, device=inp.device)
+    _ok(lib().mrs_seq_causal_conv(_p(inp), _l(inp.stride(0)), _i(col0), _i(DTYPE_CODE[inp.dtype]), _p(taps), _p(bias), _i(channels),
+                                  _i(taps.shape[1]), _i(act), _p(conv_state), _p(batch.cu_tok), _p(batch.past), _p(batch.slot),
+                                  _p(batch.seq_of_tok), _i(batch.n_seq), _i(T), _p(out), _st(inp)), "causal_conv")
+    return out
+
+
+def ssm_steps(inp, col0, bias, a_log):
+    T, H = inp.shape[0], bias.numel()
+    step = torch.empty(T, H, dtype=torch.float32, device=inp.device)
+    decay = torch.empty_like(step)
+    _ok(lib().mrs_seq_ssm_steps(_p(inp), _l(inp.stride(0)), _i(col0), _i(DTYPE_CODE[inp.dtype]), _p(bias), _p(a_log), _i(H), _i(T),
+                                _p(step), _p(decay), _st(inp)), "ssm_steps")
+    return step, decay
+
+
+def linear_scan(q, q_col, k, k_col, v, v_col, heads, qk_groups, dk, dv, state, batch, act=ACT_NONE, decay_tok=None, decay_head=None,
+                scale_tok=None, skip=None):
+    """q / k / v are column ranges (starting at *_col) of 2-D activation tensors; returns o f32 [T, heads * dv]."""
+    T = q.shape[0]
+    out = torch.empty(T, heads * dv, dtype=torch.float32, device=q.device)
+    a = ScanArgs()
+    a.q, a.k, a.v = _p(q, q_col).value, _p(k, k_col).value, _p(v, v_col).value
+    a.q_ld, a.k_ld, a.v_ld = q.stride(0), k.stride(0), v.stride(0)
+    a.dtype, a.act = DTYPE_CODE[q.dtype], act
+    a.heads, a.qk_groups, a.dk, a.dv = heads, qk_groups, dk, dv
+    a.decay_tok, a.decay_head = _p(decay_tok).value, _p(decay_head).value
+    a.scale_tok, a.skip = _p(scale_tok).value, _p(skip).value
+    a.state = state.data_ptr()
+    a.cu_tok, a.past, a.slot = batch.cu_tok.data_ptr(), batch.past.data_ptr(), batch.slot.data_ptr()
+    a.n_seq, a.n_tok, a.out = batch.n_seq, T, out.data_ptr()
+    _ok(lib().mrs_seq_linear_scan(ctypes.byref(a), _st(q)), "linear_scan")
+    return out
+
+
+def qk_norm_store(y, q_col, k_col, v_col, q_norm_w, k_norm_w, eps, heads, kv_heads, dk, dv, k_cache, v_cache, slot_of_tok):
+    T, ld = y.shape[0], y.stride(0)
+    _ok(lib().mrs_seq_qk_norm_store(_p(y, q_col), _l(ld), _p(y, k_col), _l(ld), _p(y, v_col), _l(ld), _i(DTYPE_CODE[y.dtype]),
+                                    _p(q_norm_w), _p(k_norm_w), _f(eps), _i(heads), _i(kv_heads), _i(dk), _i(dv), _p(k_cache),
+                                    _p(v_cache), _p(slot_of_tok), _i(T), _st(y)), "qk_norm_store")
+
+
+def window_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, window, batch, page_size, out, out_col=0, out_scale=1.0):
+    T = y.shape[0]
+    _ok(lib().mrs_seq_window_attention(_p(y, q_col), _l(y.stride(0)), _p(k_cache), _p(v_cache), _i(DTYPE_CODE[y.dtype]), _i(heads),
+                                       _i(kv_heads), _i(dk), _i(dv), _f(scale), _i(int(window)), _p(batch.pages), _i(batch.pages.shape[1]),
+                                       _i(page_size), _p(batch.seq_of_tok), _p(batch.pos_of_tok), _i(T), _p(out, out_col),
+                                       _l(out.stride(0)), _f(out_scale), _st(y)), "window_attention")
+
+
+def moe_route(logits, correction, n_groups, keep_groups, top, renorm=False):
+    T, E = logits.shape
+    experts = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    _ok(lib().mrs_seq_moe_route(_p(logits), _p(correction), _i(T), _i(E), _i(n_groups), _i(keep_groups), _i(top), _i(int(renorm)),
+                                _p(experts), _p(weights), _st(logits)), "moe_route")
+    return experts, weights
+
+
+def moe_small(x, gate_up, down, experts, weights, act):
+    """Expert feed-forward by weight streaming (few tokens): gate_up [E, 2ff, W], down [E, W, ff]."""
+    T, W = x.shape
+    top, ff = experts.shape[1], down.shape[2]
+    code = _i(DTYPE_CODE[x.dtype])
+    hidden = torch.empty(T * top, ff, dtype=x.dtype, device=x.device)
+    out = torch.empty(T, W, dtype=x.dtype, device=x.device)
+    _ok(lib().mrs_seq_moe_gate_up(_p(x), _p(gate_up), code, _p(experts), _i(T), _i(top), _i(W), _i(ff), _i(act), _p(hidden), _st(x)),
+        "moe_gate_up")
+    _ok(lib().mrs_seq_moe_down(_p(hidden), _p(down), code, _p(experts), _p(weights), _i(T), _i(top), _i(W), _i(ff), _p(out), _st(x)),
+        "moe_down")
+    return out
+
+
+def moe_sort(experts, n_experts):
+    n = experts.numel()
+    counts = torch.empty(n_experts, dtype=torch.int32, device=experts.device)
+    order = torch.empty(n, dtype=torch.int32, device=experts.device)
+    _ok(lib().mrs_seq_moe_sort(_p(experts), _i(n), _i(n_experts), _p(counts), _p(order), _st(experts)), "moe_sort")
+    return counts, order
+
+
+def moe_gather(x, order, top):
+    n, W = order.numel(), x.shape[1]
+    out = torch.empty(n, W, dtype=x.dtype, device=x.device)
+    _ok(lib().mrs_seq_moe_gather(_p(x), _i(DTYPE_CODE[x.dtype]), _p(order), _i(n), _i(top), _i(W), _p(out), _st(x)), "moe_gather")
+    return out
+
+
+def moe_combine(sorted_y, order, weights):
+    T, top = weights.shape
+    W = sorted_y.shape[1]
+    inverse = torch.empty(T * top, dtype=torch.int32, device=sorted_y.device)
+    out = torch.empty(T, W, dtype=sorted_y.dtype, device=sorted_y.device)
+    _ok(lib().mrs_seq_moe_combine(_p(sorted_y), _i(DTYPE_CODE[sorted_y.dtype]), _p(order), _p(weights), _i(T), _i(top), _i(W),
+                                  _p(inverse), _p(out), _st(sorted_y)), "moe_combine")
+    return out
