@@ -233,6 +233,7 @@ extern "C" int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream
   cudaStream_t st = (cudaStream_t)stream;
   if (a.dk <= 128) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 16, 16>(a, st)));
   if (a.dk <= 512) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 32, 8>(a, st)));
+  if (a.dk <= 2048) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 64, 4>(a, st)));
   return -2;
 }
 

@@ -41,9 +41,7 @@ __global__ void qk_norm_store_kernel(T *__restrict__ q, int64_t q_ld, const T *_
 // One warp per (token, head).  32 keys per round: lane j scores key j against the whole query (held in shared
 // memory as f32, pre-scaled), the round's maximum and sum go through the warp, then every lane accumulates its
 // value columns over the round's keys.  Softmax statistics and the output accumulate in f32.
-constexpr int MAX_VCOLS = 8;   // value head size up to 256
-
-template <typename T>
+template <typename T, int MAX_VCOLS>   // MAX_VCOLS * 32 >= value head size
 __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restrict__ q, int64_t q_ld, const T *__restrict__ k_cache,
                                                                const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
                                                                float scale, int window, const int32_t *__restrict__ pages,
@@ -123,12 +121,20 @@ extern "C" int mrs_seq_window_attention(const void *q, int64_t q_ld, const void 
                                         int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, int n_tok, void *out,
                                         int64_t out_ld, float out_scale, int64_t stream) {
   if (n_tok <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 32 * MAX_VCOLS || dk > 1024) return -2;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 512 || dk > 1024) return -2;
   const int warps = 4;
   const int64_t jobs = (int64_t)n_tok * heads;
-  SEQ_DISPATCH_DTYPE(dtype, (window_attention_kernel<T><<<(unsigned)((jobs + warps - 1) / warps), warps * 32,
-                                                         warps * dk * sizeof(float), (cudaStream_t)stream>>>(
-                                (const T *)q, q_ld, (const T *)k_cache, (const T *)v_cache, heads, kv_heads, dk, dv, scale, window,
-                                pages, pages_ld, page_size, seq_of_tok, pos_of_tok, n_tok, (T *)out, out_ld, out_scale)));
+#define SEQ_ATTN_LAUNCH(VC)                                                                                              \
+  window_attention_kernel<T, VC><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, warps * dk * sizeof(float),          \
+                                   (cudaStream_t)stream>>>((const T *)q, q_ld, (const T *)k_cache, (const T *)v_cache, heads, \
+                                                           kv_heads, dk, dv, scale, window, pages, pages_ld, page_size,      \
+                                                           seq_of_tok, pos_of_tok, n_tok, (T *)out, out_ld, out_scale)
+  SEQ_DISPATCH_DTYPE(dtype, {
+    if (dv <= 64) SEQ_ATTN_LAUNCH(2);
+    else if (dv <= 128) SEQ_ATTN_LAUNCH(4);
+    else if (dv <= 256) SEQ_ATTN_LAUNCH(8);
+    else SEQ_ATTN_LAUNCH(16);
+  });
+#undef SEQ_ATTN_LAUNCH
   return launch_status();
 }

@@ -127,20 +127,26 @@ class Scheduler:
 
     def plan(self, engine):
         budget, plan = self.max_step_tokens, []
+        slots_left, pages_left = engine.free_slots(), engine.free_pages()      # what this plan has not yet promised
         for r in self.running:
             n = min(len(r.tokens) - r.n_computed, budget)
-            if n > 0 and engine.can_grow(r, n):
+            need = engine.pages_needed(r, n) if n > 0 else 0
+            if n > 0 and need <= pages_left:
                 plan.append((r, n))
                 budget -= n
-        while self.waiting and budget > 0:
+                pages_left -= need
+        while self.waiting and budget > 0 and slots_left > 0:
             r = self.waiting[0]
             n = min(len(r.tokens), budget)
-            if not engine.can_admit(r, n):
+            need = engine.pages_needed(r, n)
+            if need > pages_left:
                 break
             self.waiting.popleft()
             self.running.append(r)
             plan.append((r, n))
             budget -= n
+            slots_left -= 1
+            pages_left -= need
         return plan
 
     def retire(self, req):
@@ -169,15 +175,15 @@ class Engine:
             torch.set_float32_matmul_precision("highest")
 
     # ---- capacity -------------------------------------------------------------------------------------
-    def _pages_needed(self, req, n_new):
+    def pages_needed(self, req, n_new):
         have = self.pages.num_blocks_for_request(req.rid) if self.pages.has_request(req.rid) else 0
         return max(0, -(-(req.n_computed + n_new) // self.page_size) - have)
 
-    def can_grow(self, req, n_new):
-        return self._pages_needed(req, n_new) <= self.pages.num_free_blocks()
+    def free_pages(self):
+        return self.pages.num_free_blocks()
 
-    def can_admit(self, req, n_new):
-        return self.slots.num_free() > 0 and self._pages_needed(req, n_new) <= self.pages.num_free_blocks()
+    def free_slots(self):
+        return self.slots.num_free()
 
     # ---- requests -------------------------------------------------------------------------------------
     def new_request(self, prompt, sampling=None):
@@ -236,8 +242,8 @@ class Engine:
         """One scheduler-planned step; returns [(request, new token)] for the requests that produced one."""
         plan = self.scheduler.plan(self)
         if not plan:
-            if self.scheduler.waiting:
-                raise MemoryError("a waiting request does not fit the pools even alone")
+            if self.scheduler.waiting or self.scheduler.running:
+                raise MemoryError("no live or waiting request can take its next step: the pools are too small")
             return []
         logits = self.execute(plan)
         out = []

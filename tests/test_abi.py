@@ -11,12 +11,12 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared_symbols(host=False):
-    """symbols declared by include/*.h; mrs_b200_host.h belongs to libmrs_b200_host.so, the rest to
-    the CUDA library"""
+def _declared_symbols(host=False, seq=False):
+    """symbols declared by include/*.h; mrs_b200_host.h belongs to libmrs_b200_host.so, mrs_b200_seq.h to
+    libmrs_b200_seq.so, the rest to the CUDA library"""
     names = set()
     for h in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
-        if h.endswith("_host.h") != host:
+        if h.endswith("_host.h") != host or h.endswith("_seq.h") != seq:
             continue
         src = subprocess.run(["gcc", "-E", "-P", h], capture_output=True, text=True, check=True).stdout
         src = re.sub(r"typedef\s+struct\s*\{.*?\}\s*\w+\s*;", "", src, flags=re.S)
@@ -42,6 +42,16 @@ def test_host_library_exports_its_header():
     lib = ctypes.CDLL(HOST_LIB_PATH)
     decl = _declared_symbols(host=True)
     assert len(decl) >= 26, len(decl)
+    missing = [n for n in sorted(decl) if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_sequence_mixer_library_exports_its_header():
+    from mistralrs_b200 import seq_ops
+    seq_ops.lib()      # builds it when missing
+    lib = ctypes.CDLL(seq_ops.SEQ_LIB_PATH)
+    decl = _declared_symbols(seq=True)
+    assert len(decl) >= 16, len(decl)
     missing = [n for n in sorted(decl) if not hasattr(lib, n)]
     assert not missing, missing
 
