@@ -410,6 +410,180 @@ def bench_gptq_batch32(torch, dev, peaks, steps=2, layers=0, batch=32):
 
 
 # ------------------------------------------------------------------------------------------- main
+# ------------------------------------------------------------------------------------------- --arch nisasun
+def nisasun_bench_config(width, vocab=32000):
+    """Four layers, one of each kind, at sizes of a real model's layers of this width."""
+    H = width // 128
+    light = {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * i / max(H - 1, 1)) for i in range(H)]}
+    par = {"left": {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "mask": {"size": 1024}, "scale": 128 ** -0.5},
+           "right": {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4},
+           "left_scale": 0.5, "right_scale": 0.5}
+    dense = {"kind": "dense", "ff": 4 * width}
+    moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Nisasun", "vocab": vocab, "width": width, "streams": 2, "norm": {"eps": 1e-6},
+            "layers": [{"type": "lightning", "mixer": light, "mlp": dense}, {"type": "lightning", "mixer": light, "mlp": moe},
+                       {"type": "parallel", "mixer": par, "mlp": dense}, {"type": "parallel", "mixer": par, "mlp": moe}]}
+
+
+def bench_nisasun(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), prompt=4096, decode_batches=(1, 32)):
+    """Throughput of the Nisasun design through `engine.Engine` (scheduler-free `execute`, the call `step` makes) and of the
+    Llama path at equal width / depth / feed-forward size; then every kernel of the design timed alone with CUDA events
+    (L2 flushed between repetitions) against its algorithmic bytes or flops."""
+    import numpy as np
+    from mistralrs_b200 import engine, model as M, nisasun, seq_ops as K, mixers
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    tpeak = peaks.get("bf16_tflops_sustained", 1400.0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    warmup, steps = max(3, warmup), max(1, steps)
+
+    def timed(fn, reps=steps):
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        return sorted(ts)[len(ts) // 2]
+
+    out = {"metric": "nisasun_prefill_tok_s", "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True,
+           "dtype": "bf16 (f32 residual streams, states, norms, softmax, router)", "data": "synthetic", "sizes": []}
+    for width in widths:
+        cj = nisasun_bench_config(width)
+        cfg = nisasun.NisasunConfig(cj)
+        model = nisasun.NisasunModel.random(cfg, dev, torch.bfloat16, seed=width)
+        rng = np.random.default_rng(width)
+        row = {"width": width, "layers": len(cj["layers"]), "prompt_tokens": prompt}
+        # ---- prefill: one prompt of `prompt` tokens, whole ----
+        eng = engine.Engine(model, max_tokens=max(prompt, 32 * (prompt // 8 + 64)) + 64, max_seqs=max(decode_batches))
+        toks = rng.integers(0, cfg.vocab, prompt).tolist()
+
+        def prefill():
+            r = eng.new_request(toks)
+            eng.execute([(r, prompt)])
+            eng.finish(r)
+        t = timed(prefill)
+        row["prefill_tok_s"], row["prefill_ms"] = prompt / t, t * 1e3
+        # ---- per-kernel table on the same prompt: CUDA events around every call, grouped by op ----
+        acc = {}
+
+        def wrap(mod, name):
+            f = getattr(mod, name)
+
+            def g(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = f(*a, **k)
+                e1.record()
+                acc.setdefault(name, []).append((e0, e1))
+                return r
+            setattr(mod, name, g)
+            return f
+        names = ["embed_streams", "streams_read_norm", "streams_write", "glu_split", "gated_group_norm", "causal_conv", "ssm_steps",
+                 "linear_scan", "qk_norm_store", "window_attention", "moe_route", "moe_small", "moe_sort", "moe_gather", "moe_combine"]
+        saved = {n: wrap(K, n) for n in names}
+        saved_lin = wrap(mixers, "linear")
+
+        def table():
+            acc.clear()
+            torch.cuda.synchronize()
+            return acc
+        table(); prefill(); torch.cuda.synchronize()
+        row["prefill_ms_by_op"] = {n: round(sum(a.elapsed_time(b) for a, b in v), 4) for n, v in acc.items()}
+        # ---- decode: `b` sequences with a context of prompt/8 tokens each, one token per step ----
+        row["decode"] = []
+        ctx = prompt // 8
+        for b in decode_batches:
+            reqs = [eng.new_request(rng.integers(0, cfg.vocab, ctx + 64).tolist()) for _ in range(b)]
+            eng.execute([(r, ctx) for r in reqs])
+
+            def dec():
+                eng.execute([(r, 1) for r in reqs])
+            for n, f in saved.items():
+                setattr(K, n, f)
+            setattr(mixers, "linear", saved_lin)
+            t = timed(dec, reps=max(steps, 5))
+            saved = {n: wrap(K, n) for n in names}
+            saved_lin = wrap(mixers, "linear")
+            table(); dec(); torch.cuda.synchronize()
+            row["decode"].append({"batch": b, "context": ctx, "tok_s": b / t, "ms_per_step": t * 1e3,
+                                  "ms_by_op": {n: round(sum(a.elapsed_time(c) for a, c in v), 4) for n, v in acc.items()}})
+            for r in reqs:
+                eng.finish(r)
+        for n, f in saved.items():
+            setattr(K, n, f)
+        setattr(mixers, "linear", saved_lin)
+        # ---- rooflines of the design's own kernels at this size (prefill shapes) ----
+        lm, pm = cj["layers"][0]["mixer"], cj["layers"][2]["mixer"]
+        Hh, dk, dv = lm["heads"], lm["dim"], lm["vdim"]
+        L, R = pm["left"], pm["right"]
+        ops = row["prefill_ms_by_op"]
+        n_light, n_par, n_sub = 2, 2, 8
+        roof = {}
+        scan_bytes = n_light * prompt * (2 * Hh * dk * 2 + Hh * dv * 2 + Hh * dv * 4) + n_par * prompt * ((R["heads"] * R["vdim"] + 2 * R["state"]) * 2 + R["heads"] * R["vdim"] * 4)
+        scan_flop = n_light * prompt * Hh * 4.0 * dk * dv + n_par * prompt * R["heads"] * 4.0 * R["state"] * R["vdim"]
+        roof["linear_scan"] = {"ms": ops.get("linear_scan"), "hbm_frac": scan_bytes / (ops["linear_scan"] * 1e-3) / 1e9 / hbm,
+                               "tflops_f32": scan_flop / (ops["linear_scan"] * 1e-3) / 1e12}
+        win = L["mask"]["size"]
+        attn_flop = n_par * 2.0 * L["heads"] * (L["dim"] + L["vdim"]) * sum(min(i + 1, win) for i in range(prompt))
+        roof["window_attention"] = {"ms": ops.get("window_attention"), "tflops": attn_flop / (ops["window_attention"] * 1e-3) / 1e12,
+                                    "tensor_frac": attn_flop / (ops["window_attention"] * 1e-3) / 1e12 / tpeak}
+        sw_bytes = n_sub * prompt * width * (2 * 4 * 2 + 2 + 2)          # streams read + written (f32, 2 streams), y read, next input written
+        roof["streams_write"] = {"ms": ops.get("streams_write"), "hbm_frac": sw_bytes / (ops["streams_write"] * 1e-3) / 1e9 / hbm}
+        lin_flop = 0.0
+        for Lc in cj["layers"]:
+            m = Lc["mixer"]
+            if Lc["type"] == "lightning":
+                lin_flop += 2.0 * width * (2 * m["heads"] * m["dim"] + 3 * m["heads"] * m["vdim"])
+            else:
+                a, r = m["left"], m["right"]
+                inner = r["heads"] * r["vdim"]
+                lin_flop += 2.0 * width * (a["heads"] * a["dim"] + a["kv_heads"] * (a["dim"] + a["vdim"]) + a["heads"] * a["vdim"]
+                                           + 3 * inner + 2 * r["groups"] * r["state"] + r["heads"])
+            f = Lc["mlp"]
+            lin_flop += 2.0 * width * 3 * (f["ff"] if f["kind"] == "dense" else f["expert"]["ff"] * f["router"]["top"])
+        lin_flop = lin_flop * prompt + 2.0 * width * cfg.vocab
+        roof["linear (cuBLAS)"] = {"ms": ops.get("linear"), "tflops": lin_flop / (ops["linear"] * 1e-3) / 1e12,
+                                   "tensor_frac": lin_flop / (ops["linear"] * 1e-3) / 1e12 / tpeak}
+        row["roofline"] = roof
+        del eng, model
+        torch.cuda.empty_cache()
+        # ---- the Llama path at equal size: Q8_0 prefill (tcgen05 dequant GEMMs + prompt attention), Q4_K_M decode graph ----
+        lc = M.LlamaConfig(hidden=width, inter=4 * width, n_layers=4, n_heads=width // 128, n_kv_heads=max(1, width // 512), head_dim=128,
+                           vocab=32000, max_pos=prompt + 64, quant="q8_0", name="llama-equal-size", synth_scale_exp=(-15, -13))
+        w = M.LlamaWeights(lc, dev, fast_synth=True)
+        pre = M.LlamaPrefill(w, max_tokens=prompt)
+        t = timed(lambda: pre.forward(toks))
+        row["llama_equal_size"] = {"prefill_tok_s": prompt / t, "prefill_ms": t * 1e3}
+        from mistralrs_b200 import paged_attn
+        q = torch.randn(prompt, lc.n_heads, 128, device=dev).to(torch.bfloat16)
+        k = torch.randn(prompt, lc.n_kv_heads, 128, device=dev).to(torch.bfloat16)
+        ta = timed(lambda: paged_attn.prefill_attention(q, k, k, 128 ** -0.5))
+        tw = timed(lambda: paged_attn.prefill_attention(q, k, k, 128 ** -0.5, window_left=win - 1))
+        row["llama_equal_size"]["prompt_attention_tflops"] = 2.0 * prompt * prompt * lc.n_heads * 128 / ta / 1e12
+        row["llama_equal_size"]["windowed_prompt_attention_tflops"] = attn_flop / n_par / tw / 1e12
+        del pre
+        run = M.LlamaRunner(w, batch=1, max_ctx=ctx + 64)
+        run.reset(ctx)
+        run.set_tokens([1])
+        run.capture()
+        run.reset(ctx)
+        t = timed(lambda: (run.reset(ctx), run.replay()), reps=max(steps, 5))
+        row["llama_equal_size"]["decode_b1_tok_s"] = 1.0 / t
+        del run, w
+        torch.cuda.empty_cache()
+        out["sizes"].append(row)
+    out["value"] = out["sizes"][0]["prefill_tok_s"]
+    out["ms_per_step"] = out["sizes"][0]["prefill_ms"]
+    out["config"] = {"workload": "4 layers (lightning+dense, lightning+moe, parallel+dense, parallel+moe), widths %s, %d-token prompt; decode "
+                                 "at context %d; L2 flushed between repetitions" % (list(widths), prompt, prompt // 8)}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -419,6 +593,9 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="headline workload: 1 = TinyLlama-1.1B Q4_K_M on the CPU (plumbing, no GPU), 2 = 8B Q4_K_M decode b=1 (default), "
                          "3 = 8B Q8_0 prefill 4096, 4 = Mistral-7B GPTQ b=32, 5 = Llama-3-70B Q4_K_M tensor parallel (needs --gpus 8)")
+    ap.add_argument("--arch", default="llama", choices=["llama", "nisasun"],
+                    help="nisasun: prefill / decode throughput of the Nisasun design on the step engine at layer sizes of a real model "
+                         "(random weights), beside the Llama path at equal width / depth / feed-forward size, with a per-kernel table")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model")
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("MRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -453,6 +630,9 @@ def main():
         pass
     peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
 
+    if args.arch == "nisasun":
+        print(json.dumps(bench_nisasun(torch, dev, peaks, steps=args.steps, warmup=args.warmup)))
+        return
     if args.config == 3 and world == 1:
         pf = bench_prefill_q8(M, torch, dev, peaks, layers=args.layers)
         print(json.dumps({"metric": "prefill_tok_s", "value": pf["prefill_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": 3, "warmup": 1,

@@ -37,6 +37,8 @@ int mrs_seq_streams_write(float *streams, const float *w_mix, const float *w_out
                           float unit_offset, void *next_out, int64_t stream);
 
 /* ---- elementwise / norms --------------------------------------------------------------------------- */
+/* x[t][c] = act(x[t][c]) in place for c < cols (row stride ld) */
+int mrs_seq_activate_cols(void *x, int64_t ld, int dtype, int n_tok, int cols, int act, int64_t stream);
 /* out[t][c] = act(x[t][c]) * x[t][half + c]   (x [n_tok, 2 * half]) */
 int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok, int half, int act, int64_t stream);
 /* Root-mean-square norm of f32 rows in `groups` equal parts, times weight, with a gate read from an activation
@@ -79,18 +81,21 @@ typedef struct {
 int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream);
 
 /* ---- windowed attention over a paged cache --------------------------------------------------------- */
-/* Per-head RMS norm of q (in place) and k with weights shared by the heads (NULL: no norm), then k and v of the new
+/* Per-head RMS norm of q and k (both in place) with weights shared by the heads (NULL: no norm), then k and v of the new
  * tokens go to their cache slots.  Cache: k_cache [n_slots, kv_heads, dk], v_cache [n_slots, kv_heads, dv]
  * (slot = page * page_size + offset), storage type `dtype`. */
-int mrs_seq_qk_norm_store(void *q, int64_t q_ld, const void *k, int64_t k_ld, const void *v, int64_t v_ld, int dtype,
+int mrs_seq_qk_norm_store(void *q, int64_t q_ld, void *k, int64_t k_ld, const void *v, int64_t v_ld, int dtype,
                           const float *q_norm_w, const float *k_norm_w, float eps, int heads, int kv_heads, int dk, int dv,
                           void *k_cache, void *v_cache, const int64_t *slot_of_tok, int n_tok, int64_t stream);
 /* out[t][h] = softmax_j(scale * q_t . k_j) v_j over the cached positions j of t's sequence with
- * 0 <= pos(t) - j < window (window <= 0: every earlier position), times out_scale.  pages [n_seq, pages_ld]. */
+ * 0 <= pos(t) - j < window (window <= 0: every earlier position), times out_scale.  pages [n_seq, pages_ld].
+ * tok_index (NULL: all n_tok tokens in order) lists the tokens to run: n_tok is then its length. */
 int mrs_seq_window_attention(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, int dtype, int heads,
                              int kv_heads, int dk, int dv, float scale, int window, const int32_t *pages, int pages_ld,
-                             int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, int n_tok, void *out,
-                             int64_t out_ld, float out_scale, int64_t stream);
+                             int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, const int32_t *tok_index,
+                             int n_tok, void *out, int64_t out_ld, float out_scale, int64_t stream);
+/* x[r][c] *= scale for r < rows, c < cols (row stride ld) */
+int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream);
 
 /* ---- mixture of experts ---------------------------------------------------------------------------- */
 /* scores = softmax(logits) over n_experts; choice = scores + correction (NULL: 0); experts form n_groups equal

@@ -95,23 +95,17 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T *__restrict__ x, const T *__restrict__ gate_up,
                                                           const int32_t *__restrict__ experts, int top, int width, int ff, int act,
                                                           T *__restrict__ hidden) {
-  extern __shared__ float xs[];   // [width]
+  extern __shared__ __align__(16) float xs[];   // [width]
   const int pair = blockIdx.y, tok = pair / top;
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int e = experts[pair];
   for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32<T>(x[(int64_t)tok * width + c]);
   __syncthreads();
   const T *w = gate_up + (int64_t)e * 2 * ff * width;
+  const bool vec = width % Vec16<T>::N == 0 && ((uintptr_t)gate_up % 16) == 0;
   for (int r = blockIdx.x * nw + wib; r < ff; r += gridDim.x * nw) {
-    const T *wg = w + (int64_t)r * width, *wu = w + (int64_t)(ff + r) * width;
-    float ag = 0.0f, au = 0.0f;
-    for (int c = lane; c < width; c += 32) {
-      const float xv = xs[c];
-      ag = fmaf(to_f32<T>(wg[c]), xv, ag);
-      au = fmaf(to_f32<T>(wu[c]), xv, au);
-    }
-    ag = warp_sum(ag);
-    au = warp_sum(au);
+    const float ag = warp_row_dot<T>(w + (int64_t)r * width, xs, width, lane, vec);
+    const float au = warp_row_dot<T>(w + (int64_t)(ff + r) * width, xs, width, lane, vec);
     if (lane == 0) {
       // the products leave the "matrix product" in the activation type, as the large-batch path's do
       const float gt = to_f32<T>(from_f32<T>(ag)), up = to_f32<T>(from_f32<T>(au));
@@ -125,17 +119,16 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_down_kernel(const T *__restrict__ hidden, const T *__restrict__ down,
                                                        const int32_t *__restrict__ experts, const float *__restrict__ weights, int top,
                                                        int width, int ff, T *__restrict__ out) {
-  extern __shared__ float hs[];   // [top][ff]
+  extern __shared__ __align__(16) float hs[];   // [top][ff]
   const int t = blockIdx.y, lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int c = threadIdx.x; c < top * ff; c += blockDim.x) hs[c] = to_f32<T>(hidden[(int64_t)t * top * ff + c]);
   __syncthreads();
+  const bool vec = ff % Vec16<T>::N == 0 && ((uintptr_t)down % 16) == 0;
   for (int r = blockIdx.x * nw + wib; r < width; r += gridDim.x * nw) {
     float acc = 0.0f;
     for (int k = 0; k < top; k++) {
       const T *wd = down + ((int64_t)experts[(int64_t)t * top + k] * width + r) * ff;
-      float a = 0.0f;
-      for (int c = lane; c < ff; c += 32) a = fmaf(to_f32<T>(wd[c]), hs[k * ff + c], a);
-      a = warp_sum(a);
+      const float a = warp_row_dot<T>(wd, hs + k * ff, ff, lane, vec);
       acc = fmaf(weights[(int64_t)t * top + k], to_f32<T>(from_f32<T>(a)), acc);
     }
     if (lane == 0) out[(int64_t)t * width + r] = from_f32<T>(acc);
@@ -214,7 +207,7 @@ extern "C" int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype
   SEQ_DISPATCH_DTYPE(dtype, {
     auto kern = moe_gate_up_kernel<T>;
     if (bytes > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    kern<<<dim3(bx < 64 ? bx : 64, n_tok * top), warps * 32, bytes, (cudaStream_t)stream>>>(
+    kern<<<dim3(bx < 256 ? bx : 256, n_tok * top), warps * 32, bytes, (cudaStream_t)stream>>>(
         (const T *)x, (const T *)gate_up, experts, top, width, ff, act, (T *)hidden);
   });
   return launch_status();
@@ -229,7 +222,7 @@ extern "C" int mrs_seq_moe_down(const void *hidden, const void *down, int dtype,
   SEQ_DISPATCH_DTYPE(dtype, {
     auto kern = moe_down_kernel<T>;
     if (bytes > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    kern<<<dim3(bx < 64 ? bx : 64, n_tok), warps * 32, bytes, (cudaStream_t)stream>>>(
+    kern<<<dim3(bx < 256 ? bx : 256, n_tok), warps * 32, bytes, (cudaStream_t)stream>>>(
         (const T *)hidden, (const T *)down, experts, weights, top, width, ff, (T *)out);
   });
   return launch_status();

@@ -14,25 +14,40 @@ namespace seq {
 
 // One CTA: one sequence, one head, CW state columns.  Thread (col, part) keeps rows [part * RK, part * RK + RK) of its
 // column in registers; the `parts` partitions of a column sit in neighbouring lanes, so the dot with q ends in a few
-// shuffles.  q / k / v / a / b of TC tokens are staged in shared memory per round.
+// shuffles.  Tokens go through in rounds of TC: while one round runs out of f32 shared memory, the next round's
+// q / k / v / a / b stream into a raw staging area (cp.async, 16 bytes at a time when the rows are aligned), and are
+// converted (and activated) between rounds — the global latency hides behind the token loop.
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 template <typename T, int RK, int TC>
-__global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw) {
+__global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw, int aligned) {
   extern __shared__ __align__(16) float smem[];
+  constexpr int N = 16 / (int)sizeof(T);     // elements per 16 bytes
   const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cw;
   const int t0 = a.cu_tok[b], t1 = a.cu_tok[b + 1];
   if (t1 <= t0) return;
-  const int dk = a.dk, dv = a.dv, heads = a.heads;
+  const int dk = a.dk, dv = a.dv, heads = a.heads, nth = blockDim.x;
   const int g = h / (heads / a.qk_groups);
   const int part = threadIdx.x % parts, cl = threadIdx.x / parts;
-  const int PS = RK + 4;                 // padded partition stride (floats): 16-byte aligned, conflict-free
+  constexpr int PS = RK + 4;             // padded partition stride (floats): 16-byte aligned, conflict-free
   const int dks = parts * PS;
+  const int dkr = (dk + N - 1) / N * N, cwr = (cw + N - 1) / N * N;      // raw row lengths (elements), 16-byte multiples
   float *qs = smem, *ks = qs + TC * dks, *vs = ks + TC * dks, *os = vs + TC * cw, *as = os + TC * cw, *bs = as + TC;
+  float *ra = bs + TC, *rb = ra + TC;
+  T *rq = (T *)(rb + TC), *rk = rq + TC * dkr, *rv = rk + TC * dkr;
   float *state = a.state + ((int64_t)a.slot[b] * heads + h) * dk * dv;
 
   float S[RK];
   if (a.past[b] > 0) {   // stage the tile [dk, cw] through shared memory so the global reads run along columns
     float *tile = smem;
-    for (int e = threadIdx.x; e < parts * RK * cw; e += blockDim.x) {
+    for (int e = threadIdx.x; e < parts * RK * cw; e += nth) {
       const int r = e / cw, c = e % cw;
       tile[e] = (r < dk && col0 + c < dv) ? state[(int64_t)r * dv + col0 + c] : 0.0f;
     }
@@ -44,32 +59,72 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
 #pragma unroll
     for (int r = 0; r < RK; r++) S[r] = 0.0f;
   }
+  for (int e = threadIdx.x; e < 2 * TC * dks; e += nth) qs[e] = 0.0f;     // rows past dk stay zero for good
   const float skip = a.skip ? a.skip[h] : 0.0f;
-  const T *q = (const T *)a.q, *k = (const T *)a.k, *v = (const T *)a.v;
+  const T *q = (const T *)a.q + g * dk, *k = (const T *)a.k + g * dk, *v = (const T *)a.v + h * dv + col0;
+  const int vcols = min(cw, dv - col0);
 
-  for (int c0 = t0; c0 < t1; c0 += TC) {
+  auto issue = [&](int c0) {      // round starting at token c0 -> raw staging
     const int n = min(TC, t1 - c0);
-    for (int e = threadIdx.x; e < n * parts * RK; e += blockDim.x) {
-      const int i = e / (parts * RK), d = e % (parts * RK);
-      float qv = 0.0f, kv = 0.0f;
-      if (d < dk) {
-        qv = apply_act(to_f32<T>(q[(int64_t)(c0 + i) * a.q_ld + g * dk + d]), a.act);
-        kv = apply_act(to_f32<T>(k[(int64_t)(c0 + i) * a.k_ld + g * dk + d]), a.act);
+    if (aligned) {
+      const int per = dkr / N;
+      for (int e = threadIdx.x; e < n * per; e += nth) {
+        const int i = e / per, j = e % per;
+        cp_async16(rq + i * dkr + j * N, q + (int64_t)(c0 + i) * a.q_ld + j * N);
+        cp_async16(rk + i * dkr + j * N, k + (int64_t)(c0 + i) * a.k_ld + j * N);
       }
-      const int at = i * dks + (d / RK) * PS + d % RK;
-      qs[at] = qv;
-      ks[at] = kv;
-    }
-    for (int e = threadIdx.x; e < n * cw; e += blockDim.x) {
-      const int i = e / cw, c = e % cw;
-      vs[e] = col0 + c < dv ? apply_act(to_f32<T>(v[(int64_t)(c0 + i) * a.v_ld + h * dv + col0 + c]), a.act) : 0.0f;
+      const int perv = vcols / N;
+      for (int e = threadIdx.x; e < n * perv; e += nth) {
+        const int i = e / perv, j = e % perv;
+        cp_async16(rv + i * cwr + j * N, v + (int64_t)(c0 + i) * a.v_ld + j * N);
+      }
+    } else {
+      for (int e = threadIdx.x; e < n * dk; e += nth) {
+        const int i = e / dk, d = e % dk;
+        rq[i * dkr + d] = q[(int64_t)(c0 + i) * a.q_ld + d];
+        rk[i * dkr + d] = k[(int64_t)(c0 + i) * a.k_ld + d];
+      }
+      for (int e = threadIdx.x; e < n * vcols; e += nth) {
+        const int i = e / vcols, c = e % vcols;
+        rv[i * cwr + c] = v[(int64_t)(c0 + i) * a.v_ld + c];
+      }
     }
     if (threadIdx.x < n) {
       const int64_t th = (int64_t)(c0 + threadIdx.x) * heads + h;
-      as[threadIdx.x] = a.decay_tok ? a.decay_tok[th] : a.decay_head[h];
-      bs[threadIdx.x] = a.scale_tok ? a.scale_tok[th] : 1.0f;
+      if (a.decay_tok) cp_async4(ra + threadIdx.x, a.decay_tok + th);
+      if (a.scale_tok) cp_async4(rb + threadIdx.x, a.scale_tok + th);
+    }
+    cp_async_commit();
+  };
+
+  issue(t0);
+  for (int c0 = t0; c0 < t1; c0 += TC) {
+    const int n = min(TC, t1 - c0);
+    cp_async_wait_all();
+    __syncthreads();
+    {   // raw -> f32 working set (activation applied here)
+      const int per = dkr / N;
+      for (int e = threadIdx.x; e < n * per; e += nth) {
+        const int i = e / per, d0 = (e % per) * N;
+        const int at = i * dks + (d0 / RK) * PS + d0 % RK;
+#pragma unroll
+        for (int x = 0; x < N; x++) {
+          const bool in = d0 + x < dk;
+          qs[at + x] = in ? apply_act(to_f32<T>(rq[i * dkr + d0 + x]), a.act) : 0.0f;
+          ks[at + x] = in ? apply_act(to_f32<T>(rk[i * dkr + d0 + x]), a.act) : 0.0f;
+        }
+      }
+      for (int e = threadIdx.x; e < n * cw; e += nth) {
+        const int i = e / cw, c = e % cw;
+        vs[e] = c < vcols ? apply_act(to_f32<T>(rv[i * cwr + c]), a.act) : 0.0f;
+      }
+      if (threadIdx.x < n) {
+        as[threadIdx.x] = a.decay_tok ? ra[threadIdx.x] : a.decay_head[h];
+        bs[threadIdx.x] = a.scale_tok ? rb[threadIdx.x] : 1.0f;
+      }
     }
     __syncthreads();
+    if (c0 + TC < t1) issue(c0 + TC);
     for (int i = 0; i < n; i++) {
       const float av = as[i], vv = vs[i * cw + cl], bv = bs[i] * vv;
       const float4 *kp = (const float4 *)(ks + i * dks + part * PS), *qp = (const float4 *)(qs + i * dks + part * PS);
@@ -91,18 +146,18 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
       if (part == 0) os[i * cw + cl] = fmaf(skip, vv, acc);
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < n * cw; e += blockDim.x) {
+    for (int e = threadIdx.x; e < n * cw; e += nth) {
       const int i = e / cw, c = e % cw;
-      if (col0 + c < dv) a.out[(int64_t)(c0 + i) * heads * dv + h * dv + col0 + c] = os[e];
+      if (c < vcols) a.out[(int64_t)(c0 + i) * heads * dv + h * dv + col0 + c] = os[e];
     }
-    __syncthreads();
   }
+  __syncthreads();
   {   // the state goes back the way it came
     float *tile = smem;
 #pragma unroll
     for (int r = 0; r < RK; r++) tile[(part * RK + r) * cw + cl] = S[r];
     __syncthreads();
-    for (int e = threadIdx.x; e < parts * RK * cw; e += blockDim.x) {
+    for (int e = threadIdx.x; e < parts * RK * cw; e += nth) {
       const int r = e / cw, c = e % cw;
       if (r < dk && col0 + c < dv) state[(int64_t)r * dv + col0 + c] = tile[e];
     }
@@ -111,22 +166,28 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
 
 template <typename T, int RK, int TC>
 static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
+  constexpr int N = 16 / (int)sizeof(T);
   int parts = 1;
   while (parts * RK < a.dk) parts <<= 1;
   if (parts > 32) return -2;
-  const int unit = 32 / parts;                                  // columns per warp
+  const int unit = 32 / parts > N ? 32 / parts : N;               // columns per CTA: whole warps, whole 16-byte groups
   int cw = min(256 / parts, (a.dv + unit - 1) / unit * unit);
-  const int dks = parts * (RK + 4);
-  const size_t chunk = (size_t)(2 * TC * dks + 2 * TC * cw + 2 * TC) * sizeof(float);
+  if (cw < unit) cw = unit;
+  while (cw / 2 >= unit && (cw / 2) * parts >= 64 && (int64_t)((a.dv + cw - 1) / cw) * a.heads * a.n_seq < 148) cw /= 2;   // fill the SMs
+  if (cw * parts > 256 || (cw * parts) % 32) return -2;
+  const int dks = parts * (RK + 4), dkr = (a.dk + N - 1) / N * N, cwr = (cw + N - 1) / N * N;
+  const size_t work = (size_t)(2 * TC * dks + 2 * TC * cw + 4 * TC) * sizeof(float) + (size_t)(2 * TC * dkr + TC * cwr) * sizeof(T);
   const size_t tile = (size_t)parts * RK * cw * sizeof(float);
-  const size_t bytes = chunk > tile ? chunk : tile;
+  const size_t bytes = work > tile ? work : tile;
+  const bool aligned = a.dk % N == 0 && a.dv % N == 0 && cw % N == 0 && a.q_ld % N == 0 && a.k_ld % N == 0 && a.v_ld % N == 0 &&
+                       (uintptr_t)a.q % 16 == 0 && (uintptr_t)a.k % 16 == 0 && (uintptr_t)a.v % 16 == 0;
   auto kern = linear_scan_kernel<T, RK, TC>;
   if (bytes > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((a.dv + cw - 1) / cw, a.heads, a.n_seq);
-  kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw);
+  kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw, aligned ? 1 : 0);
   return launch_status();
 }
 
@@ -213,6 +274,12 @@ __global__ void gated_group_norm_kernel(const float *__restrict__ x, const T *__
 }
 
 template <typename T>
+__global__ void activate_cols_kernel(T *__restrict__ x, int64_t ld, int cols, int act) {
+  T *row = x + (int64_t)blockIdx.x * ld;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) row[c] = from_f32<T>(apply_act(to_f32<T>(row[c]), act));
+}
+
+template <typename T>
 __global__ void glu_split_kernel(const T *__restrict__ x, T *__restrict__ out, int64_t total, int half, int act) {
   const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= total) return;
@@ -281,5 +348,11 @@ extern "C" int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok,
   if (total <= 0) return 0;
   SEQ_DISPATCH_DTYPE(dtype, (glu_split_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
                                 (const T *)x, (T *)out, total, half, act)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_activate_cols(void *x, int64_t ld, int dtype, int n_tok, int cols, int act, int64_t stream) {
+  if (n_tok <= 0 || cols <= 0) return 0;
+  SEQ_DISPATCH_DTYPE(dtype, (activate_cols_kernel<T><<<n_tok, 256, 0, (cudaStream_t)stream>>>((T *)x, ld, cols, act)));
   return launch_status();
 }

@@ -63,6 +63,43 @@ __device__ __forceinline__ float block_sum(float x, float *red) {
   return red[32];
 }
 
+// ---- 16-byte loads: dot of 16 bytes of a row with f32 values, and two neighbouring elements ----------
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+template <typename T> __device__ __forceinline__ float dot16(const float *q, const T *k);
+template <> __device__ __forceinline__ float dot16<float>(const float *q, const float *k) {
+  const float4 a = *(const float4 *)k, b = *(const float4 *)q;
+  return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
+}
+template <> __device__ __forceinline__ float dot16<__nv_bfloat16>(const float *q, const __nv_bfloat16 *k) {
+  const uint4 raw = *(const uint4 *)k;
+  const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw;
+  const float4 b0 = *(const float4 *)q, b1 = *(const float4 *)(q + 4);
+  const float2 k0 = __bfloat1622float2(h[0]), k1 = __bfloat1622float2(h[1]), k2 = __bfloat1622float2(h[2]), k3 = __bfloat1622float2(h[3]);
+  return fmaf(k0.x, b0.x, fmaf(k0.y, b0.y, fmaf(k1.x, b0.z, k1.y * b0.w))) + fmaf(k2.x, b1.x, fmaf(k2.y, b1.y, fmaf(k3.x, b1.z, k3.y * b1.w)));
+}
+template <typename T> __device__ __forceinline__ float2 load2(const T *p);
+template <> __device__ __forceinline__ float2 load2<float>(const float *p) { return *(const float2 *)p; }
+template <> __device__ __forceinline__ float2 load2<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat1622float2(*(const __nv_bfloat162 *)p); }
+
+
+// dot of one weight row (global) with x (shared, f32) across a warp; every lane gets the sum
+template <typename T>
+__device__ __forceinline__ float warp_row_dot(const T *__restrict__ w, const float *__restrict__ x, int n, int lane, bool vec) {
+  constexpr int N = Vec16<T>::N;
+  float a = 0.0f, b = 0.0f;
+  if (vec) {
+    int c = lane * N;
+    for (; c + 32 * N < n; c += 64 * N) {
+      a += dot16<T>(x + c, w + c);
+      b += dot16<T>(x + c + 32 * N, w + c + 32 * N);
+    }
+    if (c < n) a += dot16<T>(x + c, w + c);
+  } else {
+    for (int c = lane; c < n; c += 32) a = fmaf(to_f32<T>(w[c]), x[c], a);
+  }
+  return warp_sum(a + b);
+}
+
 // launch helper: a C-ABI function returns the CUDA error of its launches as an int (0 = ok)
 inline int launch_status() { return (int)cudaGetLastError(); }
 

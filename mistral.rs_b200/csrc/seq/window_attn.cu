@@ -8,7 +8,7 @@ namespace seq {
 
 // one warp per (token, head) for q; warps past the q heads take the k heads (norm + store) and the v heads (store)
 template <typename T>
-__global__ void qk_norm_store_kernel(T *__restrict__ q, int64_t q_ld, const T *__restrict__ k, int64_t k_ld, const T *__restrict__ v,
+__global__ void qk_norm_store_kernel(T *__restrict__ q, int64_t q_ld, T *__restrict__ k, int64_t k_ld, const T *__restrict__ v,
                                      int64_t v_ld, const float *__restrict__ q_norm_w, const float *__restrict__ k_norm_w,
                                      float eps, int heads, int kv_heads, int dk, int dv, T *__restrict__ k_cache,
                                      T *__restrict__ v_cache, const int64_t *__restrict__ slot_of_tok) {
@@ -18,7 +18,7 @@ __global__ void qk_norm_store_kernel(T *__restrict__ q, int64_t q_ld, const T *_
     if (job < heads + kv_heads) {
       const bool is_q = job < heads;
       const int hh = is_q ? job : job - heads;
-      const T *src = is_q ? q + (int64_t)t * q_ld + hh * dk : k + (int64_t)t * k_ld + hh * dk;
+      T *src = is_q ? q + (int64_t)t * q_ld + hh * dk : k + (int64_t)t * k_ld + hh * dk;
       const float *w = is_q ? q_norm_w : k_norm_w;
       float ss = 0.0f;
       for (int d = lane; d < dk; d += 32) {
@@ -26,9 +26,12 @@ __global__ void qk_norm_store_kernel(T *__restrict__ q, int64_t q_ld, const T *_
         ss = fmaf(x, x, ss);
       }
       const float inv = w ? rsqrtf_exact(warp_sum(ss) / (float)dk + eps) : 1.0f;
-      T *dst = is_q ? q + (int64_t)t * q_ld + hh * dk : (slot >= 0 ? k_cache + (slot * kv_heads + hh) * dk : nullptr);
-      if (dst)
-        for (int d = lane; d < dk; d += 32) dst[d] = from_f32<T>(w ? to_f32<T>(src[d]) * inv * w[d] : to_f32<T>(src[d]));
+      T *cached = (!is_q && slot >= 0) ? k_cache + (slot * kv_heads + hh) * dk : nullptr;
+      for (int d = lane; d < dk; d += 32) {   // normed in place (a prompt kernel may read q and k from here), k also to its page
+        const T r = from_f32<T>(w ? to_f32<T>(src[d]) * inv * w[d] : to_f32<T>(src[d]));
+        src[d] = r;
+        if (cached) cached[d] = r;
+      }
     } else if (slot >= 0) {
       const int hh = job - heads - kv_heads;
       const T *src = v + (int64_t)t * v_ld + hh * dv;
@@ -46,13 +49,13 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
                                                                const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
                                                                float scale, int window, const int32_t *__restrict__ pages,
                                                                int pages_ld, int page_size, const int32_t *__restrict__ seq_of_tok,
-                                                               const int32_t *__restrict__ pos_of_tok, int n_tok, T *__restrict__ out,
-                                                               int64_t out_ld, float out_scale) {
+                                                               const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index,
+                                                               int n_tok, T *__restrict__ out, int64_t out_ld, float out_scale) {
   extern __shared__ __align__(16) float qsm[];   // [warps][dk]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t job = (int64_t)blockIdx.x * (blockDim.x >> 5) + wib;
   if (job >= (int64_t)n_tok * heads) return;
-  const int t = (int)(job / heads), h = (int)(job % heads), g = h / (heads / kv_heads);
+  const int ti = (int)(job / heads), t = tok_index ? tok_index[ti] : ti, h = (int)(job % heads), g = h / (heads / kv_heads);
   const int s = seq_of_tok[t], pos = pos_of_tok[t];
   float *qv = qsm + wib * dk;
   for (int d = lane; d < dk; d += 32) qv[d] = to_f32<T>(q[(int64_t)t * q_ld + h * dk + d]) * scale;
@@ -101,34 +104,139 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
     if (c * 32 + lane < dv) out[(int64_t)t * out_ld + h * dv + c * 32 + lane] = from_f32<T>(acc[c] * inv);
 }
 
+// The same computation laid out for speed when the head sizes allow vector loads (dk a multiple of 8 and dv even):
+// one CTA of SPLIT warps per (token, head); the warps take the window's 32-key rounds in turn and their partial
+// (max, sum, output) triples are merged through shared memory.  Keys are read 16 bytes at a time, values two columns
+// per lane.
+template <typename T, int VPAIRS, int SPLIT>   // VPAIRS * 64 >= dv
+__global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
+    const T *__restrict__ q, int64_t q_ld, const T *__restrict__ k_cache, const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
+    float scale, int window, const int32_t *__restrict__ pages, int pages_ld, int page_size, const int32_t *__restrict__ seq_of_tok,
+    const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index, T *__restrict__ out, int64_t out_ld, float out_scale) {
+  extern __shared__ __align__(16) float sm[];   // q [dk] | per warp: m, l, acc [VPAIRS * 64]
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int ti = blockIdx.x / heads, h = blockIdx.x % heads, t = tok_index ? tok_index[ti] : ti, g = h / (heads / kv_heads);
+  const int s = seq_of_tok[t], pos = pos_of_tok[t];
+  float *qv = sm, *part = sm + dk;
+  for (int d = threadIdx.x; d < dk; d += SPLIT * 32) qv[d] = to_f32<T>(q[(int64_t)t * q_ld + h * dk + d]) * scale;
+  __syncthreads();
+  const int32_t *table = pages + (int64_t)s * pages_ld;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  float m = -INFINITY, l = 0.0f;
+  float2 acc[VPAIRS];
+#pragma unroll
+  for (int c = 0; c < VPAIRS; c++) acc[c] = make_float2(0.0f, 0.0f);
+  constexpr int N = Vec16<T>::N;
+  for (int j0 = lo + wib * 32; j0 <= pos; j0 += SPLIT * 32) {
+    const int j = j0 + lane;
+    float sc = -INFINITY;
+    int64_t slot = 0;
+    if (j <= pos) {
+      slot = (int64_t)table[j / page_size] * page_size + j % page_size;
+      const T *kr = k_cache + (slot * kv_heads + g) * dk;
+      float a0 = 0.0f, a1 = 0.0f;
+      int d = 0;
+      for (; d + 2 * N <= dk; d += 2 * N) {
+        a0 += dot16<T>(qv + d, kr + d);
+        a1 += dot16<T>(qv + d + N, kr + d + N);
+      }
+      for (; d < dk; d += N) a0 += dot16<T>(qv + d, kr + d);
+      sc = a0 + a1;
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    const float p = j <= pos ? expf(sc - m_new) : 0.0f;
+    const float corr = expf(m - m_new);
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int c = 0; c < VPAIRS; c++) { acc[c].x *= corr; acc[c].y *= corr; }
+    const int n = min(32, pos - j0 + 1);
+    for (int i = 0; i < n; i++) {
+      const float pi = __shfl_sync(0xffffffffu, p, i);
+      const int64_t si = __shfl_sync(0xffffffffu, slot, i);
+      const T *vr = v_cache + (si * kv_heads + g) * dv;
+#pragma unroll
+      for (int c = 0; c < VPAIRS; c++)
+        if (c * 64 + 2 * lane < dv) {
+          const float2 vv = load2<T>(vr + c * 64 + 2 * lane);
+          acc[c].x = fmaf(pi, vv.x, acc[c].x);
+          acc[c].y = fmaf(pi, vv.y, acc[c].y);
+        }
+    }
+    m = m_new;
+  }
+  float *mine = part + wib * (2 + VPAIRS * 64);
+  if (lane == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+  for (int c = 0; c < VPAIRS; c++) { mine[2 + c * 64 + 2 * lane] = acc[c].x; mine[2 + c * 64 + 2 * lane + 1] = acc[c].y; }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int w = 0; w < SPLIT; w++) mx = fmaxf(mx, part[w * (2 + VPAIRS * 64)]);
+  float lsum = 0.0f;
+  for (int w = 0; w < SPLIT; w++) {
+    const float mw = part[w * (2 + VPAIRS * 64)];
+    if (mw != -INFINITY) lsum += part[w * (2 + VPAIRS * 64) + 1] * expf(mw - mx);
+  }
+  const float inv = out_scale / lsum;
+  for (int c = threadIdx.x; c < dv; c += SPLIT * 32) {
+    float o = 0.0f;
+    for (int w = 0; w < SPLIT; w++) {
+      const float mw = part[w * (2 + VPAIRS * 64)];
+      if (mw != -INFINITY) o = fmaf(part[w * (2 + VPAIRS * 64) + 2 + c], expf(mw - mx), o);
+    }
+    out[(int64_t)t * out_ld + h * dv + c] = from_f32<T>(o * inv);
+  }
+}
+
+template <typename T>
+__global__ void scale_rows_kernel(T *__restrict__ x, int64_t ld, int cols, float scale) {
+  T *row = x + (int64_t)blockIdx.x * ld;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) row[c] = from_f32<T>(to_f32<T>(row[c]) * scale);
+}
+
 }  // namespace seq
 
 using namespace seq;
 
-extern "C" int mrs_seq_qk_norm_store(void *q, int64_t q_ld, const void *k, int64_t k_ld, const void *v, int64_t v_ld, int dtype,
+extern "C" int mrs_seq_qk_norm_store(void *q, int64_t q_ld, void *k, int64_t k_ld, const void *v, int64_t v_ld, int dtype,
                                      const float *q_norm_w, const float *k_norm_w, float eps, int heads, int kv_heads, int dk, int dv,
                                      void *k_cache, void *v_cache, const int64_t *slot_of_tok, int n_tok, int64_t stream) {
   if (n_tok <= 0) return 0;
   const int jobs = heads + 2 * kv_heads, warps = jobs < 8 ? jobs : 8;
   SEQ_DISPATCH_DTYPE(dtype, (qk_norm_store_kernel<T><<<n_tok, warps * 32, 0, (cudaStream_t)stream>>>(
-                                (T *)q, q_ld, (const T *)k, k_ld, (const T *)v, v_ld, q_norm_w, k_norm_w, eps, heads, kv_heads, dk, dv,
+                                (T *)q, q_ld, (T *)k, k_ld, (const T *)v, v_ld, q_norm_w, k_norm_w, eps, heads, kv_heads, dk, dv,
                                 (T *)k_cache, (T *)v_cache, slot_of_tok)));
   return launch_status();
 }
 
 extern "C" int mrs_seq_window_attention(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, int dtype, int heads,
                                         int kv_heads, int dk, int dv, float scale, int window, const int32_t *pages, int pages_ld,
-                                        int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, int n_tok, void *out,
-                                        int64_t out_ld, float out_scale, int64_t stream) {
+                                        int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, const int32_t *tok_index,
+                                        int n_tok, void *out, int64_t out_ld, float out_scale, int64_t stream) {
   if (n_tok <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 512 || dk > 1024) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int elem = dtype == MRS_SEQ_BF16 ? 2 : 4;
+  const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 256 && ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 8) == 0;
+  if (vec) {
+    constexpr int SPLIT = 8;
+#define SEQ_ATTN_VEC(VP)                                                                                                         \
+  window_attention_vec_kernel<T, VP, SPLIT><<<(unsigned)n_tok * heads, SPLIT * 32, (dk + SPLIT * (2 + VP * 64)) * sizeof(float), st>>>( \
+      (const T *)q, q_ld, (const T *)k_cache, (const T *)v_cache, heads, kv_heads, dk, dv, scale, window, pages, pages_ld, page_size,   \
+      seq_of_tok, pos_of_tok, tok_index, (T *)out, out_ld, out_scale)
+    SEQ_DISPATCH_DTYPE(dtype, {
+      if (dv <= 64) SEQ_ATTN_VEC(1);
+      else if (dv <= 128) SEQ_ATTN_VEC(2);
+      else SEQ_ATTN_VEC(4);
+    });
+#undef SEQ_ATTN_VEC
+    return launch_status();
+  }
   const int warps = 4;
   const int64_t jobs = (int64_t)n_tok * heads;
 #define SEQ_ATTN_LAUNCH(VC)                                                                                              \
-  window_attention_kernel<T, VC><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, warps * dk * sizeof(float),          \
-                                   (cudaStream_t)stream>>>((const T *)q, q_ld, (const T *)k_cache, (const T *)v_cache, heads, \
-                                                           kv_heads, dk, dv, scale, window, pages, pages_ld, page_size,      \
-                                                           seq_of_tok, pos_of_tok, n_tok, (T *)out, out_ld, out_scale)
+  window_attention_kernel<T, VC><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, warps * dk * sizeof(float), st>>>(  \
+      (const T *)q, q_ld, (const T *)k_cache, (const T *)v_cache, heads, kv_heads, dk, dv, scale, window, pages, pages_ld, \
+      page_size, seq_of_tok, pos_of_tok, tok_index, n_tok, (T *)out, out_ld, out_scale)
   SEQ_DISPATCH_DTYPE(dtype, {
     if (dv <= 64) SEQ_ATTN_LAUNCH(2);
     else if (dv <= 128) SEQ_ATTN_LAUNCH(4);
@@ -136,5 +244,11 @@ extern "C" int mrs_seq_window_attention(const void *q, int64_t q_ld, const void 
     else SEQ_ATTN_LAUNCH(16);
   });
 #undef SEQ_ATTN_LAUNCH
+  return launch_status();
+}
+
+extern "C" int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  SEQ_DISPATCH_DTYPE(dtype, (scale_rows_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>((T *)x, ld, cols, scale)));
   return launch_status();
 }

@@ -79,6 +79,8 @@ class StateSlots:
 class StepBatch:
     """Device-side integer description of one step.  Built on the host into one pinned buffer, copied once."""
 
+    FRESH_MIN = 32     # a sequence that starts with at least this many tokens may take the prompt-attention kernels
+
     def __init__(self, device, ids, counts, pasts, slots, tables, slot_of_tok, rows):
         n_seq, n_tok = len(counts), int(sum(counts))
         pages_ld = max(1, max(len(t) for t in tables))
@@ -89,8 +91,11 @@ class StepBatch:
         pages = np.zeros((n_seq, pages_ld), dtype=np.int32)
         for b, t in enumerate(tables):
             pages[b, :len(t)] = t
+        is_fresh = [p == 0 and c >= self.FRESH_MIN for p, c in zip(pasts, counts)]
+        self.fresh = [(int(cu[b]), int(counts[b])) for b in range(n_seq) if is_fresh[b]]      # (first row, rows) per such sequence
+        paged = np.concatenate([np.arange(cu[b], cu[b + 1], dtype=np.int32) for b in range(n_seq) if not is_fresh[b]] + [np.zeros(0, np.int32)])
         parts = [np.asarray(ids, dtype=np.int32), cu, np.asarray(pasts, dtype=np.int32), np.asarray(slots, dtype=np.int32), seq_of, pos_of,
-                 pages.reshape(-1), np.asarray(rows, dtype=np.int32)]
+                 pages.reshape(-1), np.asarray(rows, dtype=np.int32), paged]
         sizes = [p.size for p in parts]
         pad = sum(sizes) % 2                                       # keep the int64 tail 8-byte aligned
         host = torch.empty(sum(sizes) + pad + 2 * n_tok, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else \
@@ -109,6 +114,7 @@ class StepBatch:
         self.ids, self.cu_tok, self.past, self.slot, self.seq_of_tok, self.pos_of_tok = (cut(i) for i in range(6))
         self.pages = cut(6).view(n_seq, pages_ld)
         self.rows = cut(7)
+        self.paged_tok = cut(8)                                    # tokens of the sequences not in `fresh`
         self.slot_of_tok = dev[at:at + 2 * n_tok].view(torch.int64)
         self.n_seq, self.n_tok, self.h2d_bytes = n_seq, n_tok, host.numel() * 4
 

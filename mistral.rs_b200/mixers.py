@@ -40,7 +40,8 @@ class LinearAttentionMixer:
     def forward(self, h, batch, cache):
         H, dk, dv = self.heads, self.dk, self.dv
         y = linear(h, self.w_qkvg)                                         # [T, 2 H dk + 2 H dv]: q | k | v | g
-        o = K.linear_scan(y, 0, y, H * dk, y, 2 * H * dk, H, H, dk, dv, cache["state"], batch, act=self.act, decay_head=self.decay)
+        K.activate_cols(y, 0, 2 * H * dk + H * dv, self.act)                # once, not once per state tile inside the scan
+        o = K.linear_scan(y, 0, y, H * dk, y, 2 * H * dk, H, H, dk, dv, cache["state"], batch, decay_head=self.decay)
         on = torch.empty(h.shape[0], H * dv, dtype=h.dtype, device=h.device)
         K.gated_group_norm(o, y, 2 * H * dk + H * dv, self.norm_w, 1, self.eps, K.ACT_SIGMOID, False, on)
         return linear(on, self.w_o)
@@ -63,12 +64,26 @@ class WindowAttention:
                 "v": torch.zeros(n_token_slots, self.kv_heads, self.dv, dtype=dtype, device=device)}
 
     def attend(self, y, col0, batch, cache, page_size, out, out_col=0, out_scale=1.0):
-        """y holds q | k | v from column col0; writes heads * dv columns of `out` from out_col."""
+        """y holds q | k | v from column col0; writes heads * dv columns of `out` from out_col.  Keys and values of the new
+        tokens are normed and stored first.  A sequence that starts in this step with a long enough portion (batch.fresh)
+        runs on the package's prompt-attention kernels over its fresh q / k / v when they fit it (bf16, equal head sizes
+        of 64 or 128, 16-byte aligned rows); every other token — portions that continue a sequence, decoded tokens, other
+        head sizes, f32 — reads its keys from the pages."""
         kc, vc = col0 + self.heads * self.dk, col0 + self.heads * self.dk + self.kv_heads * self.dk
         K.qk_norm_store(y, col0, kc, vc, self.q_norm_w, self.k_norm_w, self.eps, self.heads, self.kv_heads, self.dk, self.dv,
                         cache["k"], cache["v"], batch.slot_of_tok)
+        tok_index = None
+        aligned = all(v % 8 == 0 for v in (y.stride(0), col0, out.stride(0), out_col))
+        if batch.fresh and y.dtype == torch.bfloat16 and self.dk == self.dv and self.dk in (64, 128) and aligned:
+            for row0, rows in batch.fresh:
+                K.fresh_prompt_attention(y, row0, rows, col0, kc, vc, self.heads, self.kv_heads, self.dk, self.scale, self.window, out, out_col)
+                if out_scale != 1.0:
+                    K.scale_rows(out, row0, rows, out_col, self.heads * self.dv, out_scale)
+            tok_index = batch.paged_tok
+            if tok_index.numel() == 0:
+                return
         K.window_attention(y, col0, cache["k"], cache["v"], self.heads, self.kv_heads, self.dk, self.dv, self.scale, self.window,
-                           batch, page_size, out, out_col, out_scale)
+                           batch, page_size, out, out_col, out_scale, tok_index)
 
 
 class StateSpaceMixer:
@@ -139,7 +154,7 @@ class RoutedExperts:
     (token, expert) pairs: two weight-streaming kernels.  Many: rows sorted by expert, one GEMM pair per expert that
     has rows (the per-expert row counts cross to the host once per layer), weighted combine in f32."""
 
-    SMALL_PAIRS = 64
+    PAIRS_PER_EXPERT = 2       # up to this many (token, expert) pairs per expert the weights are simply streamed per pair
 
     def __init__(self, w_router, correction, w_gate_up, w_down, top, n_groups, keep_groups, act, renorm=False):
         self.w_router, self.correction, self.w_gate_up, self.w_down = w_router, correction, w_gate_up, w_down
@@ -152,7 +167,7 @@ class RoutedExperts:
 
     def forward(self, h):
         experts, weights = self.route(h)
-        if experts.numel() <= self.SMALL_PAIRS:
+        if experts.numel() <= self.PAIRS_PER_EXPERT * self.n_experts:
             return K.moe_small(h, self.w_gate_up, self.w_down, experts, weights, self.act)
         counts, order = K.moe_sort(experts, self.n_experts)
         xs = K.moe_gather(h, order, self.top)

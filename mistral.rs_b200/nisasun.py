@@ -129,8 +129,10 @@ class NisasunModel:
                                         vec(p + "mix.right.conv.b"), vec(p + "mix.right.dt_bias"), vec(p + "mix.right.A_log"),
                                         vec(p + "mix.right.D"), vec(p + "mix.right.norm"), cfg.eps)
                 w_out = torch.cat([tensors[p + "mix.left.o"], tensors[p + "mix.right.o"]], dim=1).to(device=device, dtype=dtype).contiguous()
-                lay.mixer = M.ParallelMixer(attn, ssm, mat(p + "mix.left.q", p + "mix.left.k", p + "mix.left.v", p + "mix.right.in"),
-                                            w_out, float(m["left_scale"]), float(m["right_scale"]), page_size)
+                w_in = mat(p + "mix.left.q", p + "mix.left.k", p + "mix.left.v", p + "mix.right.in")
+                if w_in.shape[0] % 8:       # zero rows: the projection's rows then start on 16-byte boundaries
+                    w_in = torch.cat([w_in, w_in.new_zeros(8 - w_in.shape[0] % 8, w_in.shape[1])]).contiguous()
+                lay.mixer = M.ParallelMixer(attn, ssm, w_in, w_out, float(m["left_scale"]), float(m["right_scale"]), page_size)
             mlp = L.get("mlp")
             lay.mlp = None
             if mlp is not None:

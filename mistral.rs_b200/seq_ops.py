@@ -105,6 +105,12 @@ def streams_write(streams, w_mix, w_out, y, next_in=None, next_norm_w=None, eps=
     return nxt
 
 
+def activate_cols(x, col0, cols, act):
+    """x[:, col0:col0 + cols] = act(.) in place."""
+    _ok(lib().mrs_seq_activate_cols(_p(x, col0), _l(x.stride(0)), _i(DTYPE_CODE[x.dtype]), _i(x.shape[0]), _i(cols), _i(act), _st(x)),
+        "activate_cols")
+
+
 def glu_split(x, act):
     T, two = x.shape
     out = torch.empty(T, two // 2, dtype=x.dtype, device=x.device)
@@ -164,12 +170,33 @@ def qk_norm_store(y, q_col, k_col, v_col, q_norm_w, k_norm_w, eps, heads, kv_hea
                                     _p(v_cache), _p(slot_of_tok), _i(T), _st(y)), "qk_norm_store")
 
 
-def window_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, window, batch, page_size, out, out_col=0, out_scale=1.0):
-    T = y.shape[0]
+def window_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, window, batch, page_size, out, out_col=0, out_scale=1.0,
+                     tok_index=None):
+    """Every token of the step (or those listed in tok_index) against the pages of its sequence."""
+    n = y.shape[0] if tok_index is None else tok_index.numel()
     _ok(lib().mrs_seq_window_attention(_p(y, q_col), _l(y.stride(0)), _p(k_cache), _p(v_cache), _i(DTYPE_CODE[y.dtype]), _i(heads),
                                        _i(kv_heads), _i(dk), _i(dv), _f(scale), _i(int(window)), _p(batch.pages), _i(batch.pages.shape[1]),
-                                       _i(page_size), _p(batch.seq_of_tok), _p(batch.pos_of_tok), _i(T), _p(out, out_col),
+                                       _i(page_size), _p(batch.seq_of_tok), _p(batch.pos_of_tok), _p(tok_index), _i(n), _p(out, out_col),
                                        _l(out.stride(0)), _f(out_scale), _st(y)), "window_attention")
+
+
+def scale_rows(x, row0, rows, col0, cols, scale):
+    _ok(lib().mrs_seq_scale_rows(_p(x, row0 * x.stride(0) + col0), _l(x.stride(0)), _i(DTYPE_CODE[x.dtype]), _i(rows), _i(cols), _f(scale),
+                                 _st(x)), "scale_rows")
+
+
+def fresh_prompt_attention(y, row0, rows, q_col, k_col, v_col, heads, kv_heads, d, scale, window, out, out_col):
+    """Causal (windowed) attention of one sequence's first `rows` tokens over its own fresh q / k / v, through the
+    package's prompt-attention kernels (tcgen05 for head size 128 without a window, mma.sync otherwise; libmrs_b200.so,
+    built on first use).  q / k / v are column ranges of `y`; writes heads * d columns of `out` from out_col."""
+    from . import LIB_PATH, lib as main_lib
+    make_target(os.path.join(_HERE, "csrc"), LIB_PATH)
+    ld, at = y.stride(0), row0 * y.stride(0)
+    rc = main_lib().mrs_prefill_attention(_p(y, at + q_col), _p(y, at + k_col), _p(y, at + v_col), _p(out, row0 * out.stride(0) + out_col),
+                                          ctypes.c_void_p(0), _i(0), _i(rows), _i(rows), _i(heads), _i(kv_heads), _i(d), _l(ld), _l(ld),
+                                          _l(out.stride(0)), _f(scale), _i(1), _i(window - 1 if window > 0 else -1), _f(0.0),
+                                          ctypes.c_uint32(1), ctypes.c_void_p(torch.cuda.current_stream(y.device).cuda_stream))
+    _ok(rc, "mrs_prefill_attention")
 
 
 def moe_route(logits, correction, n_groups, keep_groups, top, renorm=False):

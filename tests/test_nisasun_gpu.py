@@ -203,6 +203,16 @@ def test_parallel_mixer_other_sizes(cuda, kw):
     close_rows(got, want, 3e-5)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("portions", [[90], [40, 1, 30, 19], [3, 87]])
+def test_parallel_mixer_prompt_kernels(cuda, d, portions):
+    """bf16 with equal head sizes of 64 / 128: a sequence's first portion of 32 tokens or more runs on the package's
+    prompt-attention kernels over the fresh q / k / v; the pages must still be filled for what follows."""
+    layer = parallel_layer(heads=4, kv_heads=2, dim=d, vdim=d, window=23, scale=d ** -0.5, s_heads=4, s_vdim=16, state=16, groups=1)
+    got, want = mixer_case(cuda, layer, torch.bfloat16, 90, portions, width=64)
+    close_rows(got, want, 3e-2)
+
+
 @pytest.mark.parametrize("distance", [-2, -1, 0, 1])
 @pytest.mark.parametrize("decoded", [False, True])
 def test_window_edge_shows(cuda, distance, decoded):
@@ -247,7 +257,7 @@ def test_dense_ff(cuda, dtype, tol):
 
 @pytest.mark.parametrize("kw", [dict(), dict(experts=12, top=4, count=2, keep=1), dict(experts=6, top=6, count=3, keep=3), dict(experts=5, top=1, count=1, keep=1),
                                 dict(experts=16, top=2, count=8, keep=3)])
-@pytest.mark.parametrize("T", [3, 150])     # few pairs: weight-streaming kernels; many: rows sorted by expert
+@pytest.mark.parametrize("T", [3, 150])     # few pairs per expert: weight-streaming kernels; many: rows sorted by expert
 def test_routed_experts(cuda, kw, T):
     mlp = moe(**kw)
 
