@@ -484,7 +484,7 @@ def bench_nisasun(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
             setattr(mod, name, g)
             return f
         names = ["embed_streams", "streams_read_norm", "streams_write", "glu_split", "gated_group_norm", "causal_conv", "ssm_steps",
-                 "linear_scan", "qk_norm_store", "window_attention", "moe_route", "moe_small", "moe_sort", "moe_gather", "moe_combine"]
+                 "linear_scan", "qk_norm_store", "window_attention", "fresh_prompt_attention", "scale_rows", "activate_cols", "moe_route", "moe_small", "moe_sort", "moe_gather", "moe_combine"]
         saved = {n: wrap(K, n) for n in names}
         saved_lin = wrap(mixers, "linear")
 
@@ -530,8 +530,10 @@ def bench_nisasun(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
                                "tflops_f32": scan_flop / (ops["linear_scan"] * 1e-3) / 1e12}
         win = L["mask"]["size"]
         attn_flop = n_par * 2.0 * L["heads"] * (L["dim"] + L["vdim"]) * sum(min(i + 1, win) for i in range(prompt))
-        roof["window_attention"] = {"ms": ops.get("window_attention"), "tflops": attn_flop / (ops["window_attention"] * 1e-3) / 1e12,
-                                    "tensor_frac": attn_flop / (ops["window_attention"] * 1e-3) / 1e12 / tpeak}
+        attn_ms = ops.get("fresh_prompt_attention", 0.0) + ops.get("window_attention", 0.0) + ops.get("scale_rows", 0.0)
+        roof["window_attention (prompt)"] = {"ms": attn_ms, "tflops": attn_flop / (attn_ms * 1e-3) / 1e12,
+                                             "tensor_frac": attn_flop / (attn_ms * 1e-3) / 1e12 / tpeak,
+                                             "kernel": "prompt-attention kernels over fresh q/k/v" if "fresh_prompt_attention" in ops else "paged kernel"}
         sw_bytes = n_sub * prompt * width * (2 * 4 * 2 + 2 + 2)          # streams read + written (f32, 2 streams), y read, next input written
         roof["streams_write"] = {"ms": ops.get("streams_write"), "hbm_frac": sw_bytes / (ops["streams_write"] * 1e-3) / 1e9 / hbm}
         lin_flop = 0.0

@@ -66,7 +66,11 @@ int mrs_seq_ssm_steps(const void *in, int64_t in_ld, int col0, int dtype, const 
  *   o_t = S_t^T q_t + skip[h] v_t         (o f32 [n_tok, heads * dv])
  * a_t = decay_tok[t][h] (or decay_head[h] when decay_tok is NULL), b_t = scale_tok[t][h] (1 when NULL), skip NULL: 0.
  * q, k: [n_tok, qk_groups, dk] with row strides q_ld / k_ld; v: [n_tok, heads, dv] with row stride v_ld; `act` is
- * applied to q, k and v as they are read. */
+ * applied to q, k and v as they are read.
+ * Long portions can run as n_segs segments of seg_len tokens side by side (n_segs > 1): the caller provides
+ * seg_state f32 [n_seq * n_segs, heads, dk, dv] and seg_decay f32 [n_seq * n_segs, heads] as scratch; every segment is
+ * first advanced from a zero state, the segments are chained (with the slot's state) into true start states, then
+ * every segment runs again from its start and writes its outputs.  n_segs <= 1: one pass. */
 typedef struct {
   const void *q, *k, *v;
   int64_t q_ld, k_ld, v_ld;
@@ -77,6 +81,8 @@ typedef struct {
   const int32_t *cu_tok, *past, *slot;
   int n_seq, n_tok;
   float *out;
+  float *seg_state, *seg_decay;
+  int seg_len, n_segs;
 } mrs_seq_scan_args;
 int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream);
 

@@ -206,7 +206,11 @@ extern "C" int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype
   const size_t bytes = (size_t)width * sizeof(float);
   SEQ_DISPATCH_DTYPE(dtype, {
     auto kern = moe_gate_up_kernel<T>;
-    if (bytes > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    static size_t allowed = 48 * 1024;
+    if (bytes > allowed) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+      allowed = bytes;
+    }
     kern<<<dim3(bx < 256 ? bx : 256, n_tok * top), warps * 32, bytes, (cudaStream_t)stream>>>(
         (const T *)x, (const T *)gate_up, experts, top, width, ff, act, (T *)hidden);
   });
@@ -221,7 +225,11 @@ extern "C" int mrs_seq_moe_down(const void *hidden, const void *down, int dtype,
   const int warps = 8, bx = (width + warps - 1) / warps;
   SEQ_DISPATCH_DTYPE(dtype, {
     auto kern = moe_down_kernel<T>;
-    if (bytes > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    static size_t allowed = 48 * 1024;
+    if (bytes > allowed) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+      allowed = bytes;
+    }
     kern<<<dim3(bx < 256 ? bx : 256, n_tok), warps * 32, bytes, (cudaStream_t)stream>>>(
         (const T *)hidden, (const T *)down, experts, weights, top, width, ff, (T *)out);
   });

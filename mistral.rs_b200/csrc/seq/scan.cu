@@ -27,11 +27,20 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 template <typename T, int RK, int TC>
-__global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw, int aligned) {
+__global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw, int aligned, int mode) {
+  // mode 0: the whole portion of a sequence, state from / to its slot.  Long portions are cut into segments of
+  // a.seg_len tokens that run side by side: mode 1 advances a ZERO state over one segment and leaves it, with the
+  // segment's product of decays, in a.seg_state / a.seg_decay; a small kernel then chains the segments (and the slot's
+  // state) into every segment's true start state; mode 2 runs the segment again from that start and writes the outputs.
   extern __shared__ __align__(16) float smem[];
   constexpr int N = 16 / (int)sizeof(T);     // elements per 16 bytes
-  const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cw;
-  const int t0 = a.cu_tok[b], t1 = a.cu_tok[b + 1];
+  const int b = mode ? blockIdx.z / a.n_segs : blockIdx.z, seg = mode ? blockIdx.z % a.n_segs : 0;
+  const int h = blockIdx.y, col0 = blockIdx.x * cw;
+  int t0 = a.cu_tok[b], t1 = a.cu_tok[b + 1];
+  if (mode) {
+    t0 += seg * a.seg_len;
+    t1 = min(t1, t0 + a.seg_len);
+  }
   if (t1 <= t0) return;
   const int dk = a.dk, dv = a.dv, heads = a.heads, nth = blockDim.x;
   const int g = h / (heads / a.qk_groups);
@@ -42,10 +51,11 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
   float *qs = smem, *ks = qs + TC * dks, *vs = ks + TC * dks, *os = vs + TC * cw, *as = os + TC * cw, *bs = as + TC;
   float *ra = bs + TC, *rb = ra + TC;
   T *rq = (T *)(rb + TC), *rk = rq + TC * dkr, *rv = rk + TC * dkr;
-  float *state = a.state + ((int64_t)a.slot[b] * heads + h) * dk * dv;
+  float *state = mode ? a.seg_state + ((int64_t)blockIdx.z * heads + h) * dk * dv : a.state + ((int64_t)a.slot[b] * heads + h) * dk * dv;
+  float decay_product = 1.0f;
 
   float S[RK];
-  if (a.past[b] > 0) {   // stage the tile [dk, cw] through shared memory so the global reads run along columns
+  if (mode == 2 || (mode == 0 && a.past[b] > 0)) {   // stage the tile [dk, cw] through shared memory so the global reads run along columns
     float *tile = smem;
     for (int e = threadIdx.x; e < parts * RK * cw; e += nth) {
       const int r = e / cw, c = e % cw;
@@ -125,34 +135,59 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
     }
     __syncthreads();
     if (c0 + TC < t1) issue(c0 + TC);
-    for (int i = 0; i < n; i++) {
-      const float av = as[i], vv = vs[i * cw + cl], bv = bs[i] * vv;
-      const float4 *kp = (const float4 *)(ks + i * dks + part * PS), *qp = (const float4 *)(qs + i * dks + part * PS);
-      float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+    // four tokens per pass: the state's chain through them is short (two dependent operations per token and row), while
+    // their shared-memory reads, dot products and shuffle trees are independent and overlap
+    for (int i0 = 0; i0 < n; i0 += 4) {
+      float av[4], bv[4], vv[4], acc[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const bool live = i0 + u < n;          // a missing token leaves the state alone (rows past n hold old, finite data)
+        vv[u] = vs[(i0 + u) * cw + cl];
+        av[u] = live ? as[i0 + u] : 1.0f;
+        bv[u] = live ? bs[i0 + u] * vv[u] : 0.0f;
+        acc[u] = 0.0f;
+        decay_product *= av[u];
+      }
 #pragma unroll
       for (int r = 0; r < RK; r += 4) {
-        const float4 k4 = kp[r / 4], q4 = qp[r / 4];
-        S[r] = fmaf(k4.x, bv, av * S[r]);
-        S[r + 1] = fmaf(k4.y, bv, av * S[r + 1]);
-        S[r + 2] = fmaf(k4.z, bv, av * S[r + 2]);
-        S[r + 3] = fmaf(k4.w, bv, av * S[r + 3]);
-        acc0 = fmaf(S[r], q4.x, acc0);
-        acc1 = fmaf(S[r + 1], q4.y, acc1);
-        acc2 = fmaf(S[r + 2], q4.z, acc2);
-        acc3 = fmaf(S[r + 3], q4.w, acc3);
+        float4 k4[4], q4[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          k4[u] = *(const float4 *)(ks + (i0 + u) * dks + part * PS + r);
+          if (mode != 1) q4[u] = *(const float4 *)(qs + (i0 + u) * dks + part * PS + r);
+        }
+        float s0 = S[r], s1 = S[r + 1], s2 = S[r + 2], s3 = S[r + 3];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          s0 = fmaf(k4[u].x, bv[u], av[u] * s0);
+          s1 = fmaf(k4[u].y, bv[u], av[u] * s1);
+          s2 = fmaf(k4[u].z, bv[u], av[u] * s2);
+          s3 = fmaf(k4[u].w, bv[u], av[u] * s3);
+          if (mode != 1) acc[u] = fmaf(s0, q4[u].x, fmaf(s1, q4[u].y, fmaf(s2, q4[u].z, fmaf(s3, q4[u].w, acc[u]))));
+        }
+        S[r] = s0; S[r + 1] = s1; S[r + 2] = s2; S[r + 3] = s3;
       }
-      float acc = (acc0 + acc1) + (acc2 + acc3);
-      for (int m = 1; m < parts; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-      if (part == 0) os[i * cw + cl] = fmaf(skip, vv, acc);
+      if (mode != 1)
+        for (int m = 1; m < parts; m <<= 1) {
+#pragma unroll
+          for (int u = 0; u < 4; u++) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
+        }
+      if (part == 0 && mode != 1) {
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+          if (i0 + u < n) os[(i0 + u) * cw + cl] = fmaf(skip, vv[u], acc[u]);
+      }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < n * cw; e += nth) {
-      const int i = e / cw, c = e % cw;
-      if (c < vcols) a.out[(int64_t)(c0 + i) * heads * dv + h * dv + col0 + c] = os[e];
-    }
+    if (mode != 1)
+      for (int e = threadIdx.x; e < n * cw; e += nth) {
+        const int i = e / cw, c = e % cw;
+        if (c < vcols) a.out[(int64_t)(c0 + i) * heads * dv + h * dv + col0 + c] = os[e];
+      }
   }
   __syncthreads();
-  {   // the state goes back the way it came
+  if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) a.seg_decay[(int64_t)blockIdx.z * heads + h] = decay_product;
+  if (mode != 2) {   // the state goes back the way it came
     float *tile = smem;
 #pragma unroll
     for (int r = 0; r < RK; r++) tile[(part * RK + r) * cw + cl] = S[r];
@@ -164,6 +199,25 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
   }
 }
 
+// chains the segments of every sequence: seg_state[seg] <- the state before segment seg; the slot gets the final state
+__global__ void scan_chain_kernel(const mrs_seq_scan_args a) {
+  const int b = blockIdx.z, h = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x, per = a.dk * a.dv;
+  if (e >= per) return;
+  const int len = a.cu_tok[b + 1] - a.cu_tok[b];
+  if (len <= 0) return;
+  const int nseg = (len + a.seg_len - 1) / a.seg_len;
+  float *slot_state = a.state + ((int64_t)a.slot[b] * a.heads + h) * per + e;
+  float run = a.past[b] > 0 ? *slot_state : 0.0f;
+  for (int s = 0; s < nseg; s++) {
+    const int64_t z = (int64_t)b * a.n_segs + s;
+    float *p = a.seg_state + (z * a.heads + h) * per + e;
+    const float local = *p;
+    *p = run;
+    run = fmaf(a.seg_decay[z * a.heads + h], run, local);
+  }
+  *slot_state = run;
+}
+
 template <typename T, int RK, int TC>
 static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
   constexpr int N = 16 / (int)sizeof(T);
@@ -173,7 +227,7 @@ static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
   const int unit = 32 / parts > N ? 32 / parts : N;               // columns per CTA: whole warps, whole 16-byte groups
   int cw = min(256 / parts, (a.dv + unit - 1) / unit * unit);
   if (cw < unit) cw = unit;
-  while (cw / 2 >= unit && (cw / 2) * parts >= 64 && (int64_t)((a.dv + cw - 1) / cw) * a.heads * a.n_seq < 148) cw /= 2;   // fill the SMs
+  while (cw / 2 >= unit && (cw / 2) * parts >= 64 && (int64_t)((a.dv + cw - 1) / cw) * a.heads * a.n_seq * (a.n_segs > 1 ? a.n_segs : 1) < 148) cw /= 2;   // fill the SMs
   if (cw * parts > 256 || (cw * parts) % 32) return -2;
   const int dks = parts * (RK + 4), dkr = (a.dk + N - 1) / N * N, cwr = (cw + N - 1) / N * N;
   const size_t work = (size_t)(2 * TC * dks + 2 * TC * cw + 4 * TC) * sizeof(float) + (size_t)(2 * TC * dkr + TC * cwr) * sizeof(T);
@@ -182,12 +236,22 @@ static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
   const bool aligned = a.dk % N == 0 && a.dv % N == 0 && cw % N == 0 && a.q_ld % N == 0 && a.k_ld % N == 0 && a.v_ld % N == 0 &&
                        (uintptr_t)a.q % 16 == 0 && (uintptr_t)a.k % 16 == 0 && (uintptr_t)a.v % 16 == 0;
   auto kern = linear_scan_kernel<T, RK, TC>;
-  if (bytes > 48 * 1024) {
+  static size_t allowed = 48 * 1024;      // per instantiation; raised once per size, so a captured step repeats no attribute call
+  if (bytes > allowed) {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return (int)e;
+    allowed = bytes;
+  }
+  if (a.n_segs > 1 && a.seg_state && a.seg_decay && a.seg_len > 0) {
+    dim3 grid((a.dv + cw - 1) / cw, a.heads, a.n_seq * a.n_segs);
+    kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw, aligned ? 1 : 0, 1);
+    const int per = a.dk * a.dv;
+    scan_chain_kernel<<<dim3((per + 255) / 256, a.heads, a.n_seq), 256, 0, st>>>(a);
+    kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw, aligned ? 1 : 0, 2);
+    return launch_status();
   }
   dim3 grid((a.dv + cw - 1) / cw, a.heads, a.n_seq);
-  kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw, aligned ? 1 : 0);
+  kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw, aligned ? 1 : 0, 0);
   return launch_status();
 }
 
@@ -274,18 +338,30 @@ __global__ void gated_group_norm_kernel(const float *__restrict__ x, const T *__
 }
 
 template <typename T>
-__global__ void activate_cols_kernel(T *__restrict__ x, int64_t ld, int cols, int act) {
+__global__ void activate_cols_kernel(T *__restrict__ x, int64_t ld, int cols, int act, int vec) {
   T *row = x + (int64_t)blockIdx.x * ld;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) row[c] = from_f32<T>(apply_act(to_f32<T>(row[c]), act));
+  if (vec) {
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < cols; c += gridDim.y * blockDim.x * 4)
+      store4<T>(row + c, act4(load4<T>(row + c), act));
+  } else {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cols; c += gridDim.y * blockDim.x)
+      row[c] = from_f32<T>(apply_act(to_f32<T>(row[c]), act));
+  }
 }
 
 template <typename T>
-__global__ void glu_split_kernel(const T *__restrict__ x, T *__restrict__ out, int64_t total, int half, int act) {
-  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= total) return;
-  const int64_t t = e / half, c = e % half;
-  const float gt = to_f32<T>(x[t * 2 * half + c]), up = to_f32<T>(x[t * 2 * half + half + c]);
-  out[e] = from_f32<T>(apply_act(gt, act) * up);
+__global__ void glu_split_kernel(const T *__restrict__ x, T *__restrict__ out, int half, int act, int vec) {
+  const T *row = x + (int64_t)blockIdx.x * 2 * half;
+  T *dst = out + (int64_t)blockIdx.x * half;
+  if (vec) {
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < half; c += gridDim.y * blockDim.x * 4) {
+      const float4 g = act4(load4<T>(row + c), act), u = load4<T>(row + half + c);
+      store4<T>(dst + c, make_float4(g.x * u.x, g.y * u.y, g.z * u.z, g.w * u.w));
+    }
+  } else {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < half; c += gridDim.y * blockDim.x)
+      dst[c] = from_f32<T>(apply_act(to_f32<T>(row[c]), act) * to_f32<T>(row[half + c]));
+  }
 }
 
 }  // namespace seq
@@ -344,15 +420,18 @@ extern "C" int mrs_seq_gated_group_norm(const float *x, const void *gate, int64_
 }
 
 extern "C" int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok, int half, int act, int64_t stream) {
-  const int64_t total = (int64_t)n_tok * half;
-  if (total <= 0) return 0;
-  SEQ_DISPATCH_DTYPE(dtype, (glu_split_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-                                (const T *)x, (T *)out, total, half, act)));
+  if (n_tok <= 0 || half <= 0) return 0;
+  const int vec = half % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0;
+  const int per = vec ? 1024 : 256, by = (half + per - 1) / per;
+  SEQ_DISPATCH_DTYPE(dtype, (glu_split_kernel<T><<<dim3(n_tok, by < 64 ? by : 64), 256, 0, (cudaStream_t)stream>>>(
+                                (const T *)x, (T *)out, half, act, vec)));
   return launch_status();
 }
 
 extern "C" int mrs_seq_activate_cols(void *x, int64_t ld, int dtype, int n_tok, int cols, int act, int64_t stream) {
   if (n_tok <= 0 || cols <= 0) return 0;
-  SEQ_DISPATCH_DTYPE(dtype, (activate_cols_kernel<T><<<n_tok, 256, 0, (cudaStream_t)stream>>>((T *)x, ld, cols, act)));
+  const int vec = cols % 4 == 0 && ld % 4 == 0 && (uintptr_t)x % 16 == 0;
+  const int per = vec ? 1024 : 256, by = (cols + per - 1) / per;
+  SEQ_DISPATCH_DTYPE(dtype, (activate_cols_kernel<T><<<dim3(n_tok, by < 64 ? by : 64), 256, 0, (cudaStream_t)stream>>>((T *)x, ld, cols, act, vec)));
   return launch_status();
 }

@@ -82,6 +82,27 @@ template <> __device__ __forceinline__ float2 load2<float>(const float *p) { ret
 template <> __device__ __forceinline__ float2 load2<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat1622float2(*(const __nv_bfloat162 *)p); }
 
 
+// four neighbouring elements (the pointer is 4-element aligned)
+template <typename T> __device__ __forceinline__ float4 load4(const T *p);
+template <> __device__ __forceinline__ float4 load4<float>(const float *p) { return *(const float4 *)p; }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16 *p) {
+  const uint2 raw = *(const uint2 *)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *)&raw.x), b = __bfloat1622float2(*(const __nv_bfloat162 *)&raw.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void store4(T *p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float *p, float4 v) { *(float4 *)p = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16 *p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *(const uint32_t *)&a;
+  raw.y = *(const uint32_t *)&b;
+  *(uint2 *)p = raw;
+}
+__device__ __forceinline__ float4 act4(float4 v, int act) {
+  return make_float4(apply_act(v.x, act), apply_act(v.y, act), apply_act(v.z, act), apply_act(v.w, act));
+}
+
 // dot of one weight row (global) with x (shared, f32) across a warp; every lane gets the sum
 template <typename T>
 __device__ __forceinline__ float warp_row_dot(const T *__restrict__ w, const float *__restrict__ x, int n, int lane, bool vec) {

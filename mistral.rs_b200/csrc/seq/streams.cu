@@ -50,8 +50,9 @@ __global__ void streams_read_norm_kernel(const float *__restrict__ streams, cons
   }
 }
 
-// x_r <- sum_s mix[s][r] x_s + w_out[r] y, every r from the old x; then (optionally) the next read + norm
-template <typename T>
+// x_r <- sum_s mix[s][r] x_s + w_out[r] y, every r from the old x; then (optionally) the next read + norm.
+// VEC = 4: four neighbouring columns per thread (16-byte stream accesses) when the width allows; VEC = 1 otherwise.
+template <typename T, int VEC>
 __global__ void streams_write_kernel(float *__restrict__ streams, const float *__restrict__ w_mix, const float *__restrict__ w_out,
                                      const T *__restrict__ y, int n_streams, int width, const float *__restrict__ next_in,
                                      const float *__restrict__ next_norm_w, float eps, float unit_offset, T *__restrict__ next_out) {
@@ -66,34 +67,56 @@ __global__ void streams_write_kernel(float *__restrict__ streams, const float *_
   __syncthreads();
   float *x = streams + (int64_t)t * n_streams * width;
   float ss = 0.0f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float old[MAX_STREAMS];
+  for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+    float old[MAX_STREAMS][VEC], yv[VEC], u[VEC];
 #pragma unroll
     for (int s = 0; s < MAX_STREAMS; s++)
-      if (s < n_streams) old[s] = x[(int64_t)s * width + c];
-    const float yv = to_f32<T>(y[(int64_t)t * width + c]);
-    float u = 0.0f;
+      if (s < n_streams) {
+        if (VEC == 4) { const float4 v = *(const float4 *)(x + (int64_t)s * width + c); old[s][0] = v.x; old[s][1 % VEC] = v.y; old[s][2 % VEC] = v.z; old[s][3 % VEC] = v.w; }
+        else old[s][0] = x[(int64_t)s * width + c];
+      }
+    if (VEC == 4) { const float4 v = load4<T>(y + (int64_t)t * width + c); yv[0] = v.x; yv[1 % VEC] = v.y; yv[2 % VEC] = v.z; yv[3 % VEC] = v.w; }
+    else yv[0] = to_f32<T>(y[(int64_t)t * width + c]);
+#pragma unroll
+    for (int e = 0; e < VEC; e++) u[e] = 0.0f;
 #pragma unroll
     for (int r = 0; r < MAX_STREAMS; r++) {
       if (r < n_streams) {
-        float acc = wout[r] * yv;
+        float acc[VEC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; s++)
-          if (s < n_streams) acc = fmaf(mix[s * n_streams + r], old[s], acc);
-        x[(int64_t)r * width + c] = acc;
-        u = fmaf(nin[r], acc, u);
+        for (int e = 0; e < VEC; e++) {
+          acc[e] = wout[r] * yv[e];
+#pragma unroll
+          for (int s = 0; s < MAX_STREAMS; s++)
+            if (s < n_streams) acc[e] = fmaf(mix[s * n_streams + r], old[s][e], acc[e]);
+          u[e] = fmaf(nin[r], acc[e], u[e]);
+        }
+        if (VEC == 4) *(float4 *)(x + (int64_t)r * width + c) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+        else x[(int64_t)r * width + c] = acc[0];
       }
     }
-    ss = fmaf(u, u, ss);
+#pragma unroll
+    for (int e = 0; e < VEC; e++) ss = fmaf(u[e], u[e], ss);
   }
   if (next_out == nullptr) return;
   const float inv = rsqrtf_exact(block_sum(ss, red) / (float)width + eps);
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {   // the thread re-reads the columns it wrote itself
-    float u = 0.0f;
+  for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {   // the thread re-reads the columns it wrote itself
+    float u[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; e++) u[e] = 0.0f;
 #pragma unroll
     for (int r = 0; r < MAX_STREAMS; r++)
-      if (r < n_streams) u = fmaf(nin[r], x[(int64_t)r * width + c], u);
-    next_out[(int64_t)t * width + c] = from_f32<T>(u * inv * (unit_offset + next_norm_w[c]));
+      if (r < n_streams) {
+#pragma unroll
+        for (int e = 0; e < VEC; e++) u[e] = fmaf(nin[r], x[(int64_t)r * width + c + e], u[e]);
+      }
+    if (VEC == 4) {
+      const float4 w = *(const float4 *)(next_norm_w + c);
+      store4<T>(next_out + (int64_t)t * width + c, make_float4(u[0] * inv * (unit_offset + w.x), u[1 % VEC] * inv * (unit_offset + w.y),
+                                                               u[2 % VEC] * inv * (unit_offset + w.z), u[3 % VEC] * inv * (unit_offset + w.w)));
+    } else {
+      next_out[(int64_t)t * width + c] = from_f32<T>(u[0] * inv * (unit_offset + next_norm_w[c]));
+    }
   }
 }
 
@@ -127,8 +150,16 @@ extern "C" int mrs_seq_streams_write(float *streams, const float *w_mix, const f
                                      float unit_offset, void *next_out, int64_t stream) {
   if (n_tok <= 0) return 0;
   if (n_streams < 1 || n_streams > MAX_STREAMS) return -2;
-  SEQ_DISPATCH_DTYPE(dtype, (streams_write_kernel<T><<<n_tok, threads_for(width), 0, (cudaStream_t)stream>>>(
-                                streams, w_mix, w_out, (const T *)y, n_streams, width, next_in, next_norm_w, eps, unit_offset,
-                                (T *)next_out)));
+  const bool vec = width % 4 == 0 && (uintptr_t)streams % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)next_out % 16 == 0 &&
+                   (uintptr_t)next_norm_w % 16 == 0;
+  const int th = vec ? (width >= 4096 ? 256 : (width >= 512 ? 128 : 64)) : threads_for(width);
+  SEQ_DISPATCH_DTYPE(dtype, {
+    if (vec)
+      streams_write_kernel<T, 4><<<n_tok, th, 0, (cudaStream_t)stream>>>(streams, w_mix, w_out, (const T *)y, n_streams, width, next_in,
+                                                                        next_norm_w, eps, unit_offset, (T *)next_out);
+    else
+      streams_write_kernel<T, 1><<<n_tok, th, 0, (cudaStream_t)stream>>>(streams, w_mix, w_out, (const T *)y, n_streams, width, next_in,
+                                                                        next_norm_w, eps, unit_offset, (T *)next_out);
+  });
   return launch_status();
 }

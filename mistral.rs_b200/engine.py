@@ -81,9 +81,23 @@ class StepBatch:
 
     FRESH_MIN = 32     # a sequence that starts with at least this many tokens may take the prompt-attention kernels
 
-    def __init__(self, device, ids, counts, pasts, slots, tables, slot_of_tok, rows):
+    def __init__(self, device, ids, counts, pasts, slots, tables, slot_of_tok, rows, pages_ld=None):
+        self.device, self._pages_ld = device, pages_ld
+        host, layout = self._pack(ids, counts, pasts, slots, tables, slot_of_tok, rows)
+        self._host, self._dev = host, host.to(device, non_blocking=True)
+        self._bind(layout)
+
+    def refill(self, ids, counts, pasts, slots, tables, slot_of_tok, rows):
+        """The same shapes with new contents, into the same device memory (a captured graph reads it in place)."""
+        host, layout = self._pack(ids, counts, pasts, slots, tables, slot_of_tok, rows)
+        if host.numel() != self._dev.numel() or layout != self._layout:
+            raise ValueError("refill needs the sizes the batch was made with")
+        self._host = host
+        self._dev.copy_(host, non_blocking=True)
+
+    def _pack(self, ids, counts, pasts, slots, tables, slot_of_tok, rows):
         n_seq, n_tok = len(counts), int(sum(counts))
-        pages_ld = max(1, max(len(t) for t in tables))
+        pages_ld = self._pages_ld or max(1, max(len(t) for t in tables))
         cu = np.zeros(n_seq + 1, dtype=np.int32)
         cu[1:] = np.cumsum(counts)
         seq_of = np.repeat(np.arange(n_seq, dtype=np.int32), counts)
@@ -98,8 +112,8 @@ class StepBatch:
                  pages.reshape(-1), np.asarray(rows, dtype=np.int32), paged]
         sizes = [p.size for p in parts]
         pad = sum(sizes) % 2                                       # keep the int64 tail 8-byte aligned
-        host = torch.empty(sum(sizes) + pad + 2 * n_tok, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else \
-            torch.empty(sum(sizes) + pad + 2 * n_tok, dtype=torch.int32)
+        total = sum(sizes) + pad + 2 * n_tok
+        host = torch.empty(total, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else torch.empty(total, dtype=torch.int32)
         hv = host.numpy()
         at = 0
         for p in parts:
@@ -107,16 +121,42 @@ class StepBatch:
             at += p.size
         at += pad
         hv[at:at + 2 * n_tok] = np.asarray(slot_of_tok, dtype=np.int64).view(np.int32)
-        dev = host.to(device, non_blocking=True)
-        self._host, self._dev = host, dev
+        self.n_seq, self.n_tok, self.h2d_bytes = n_seq, n_tok, total * 4
+        self.longest = int(max(counts)) if n_seq else 0            # host-side facts the mixers plan with
+        return host, (tuple(sizes), pad, n_seq, n_tok, pages_ld)
+
+    def _bind(self, layout):
+        sizes, pad, n_seq, n_tok, pages_ld = layout
+        self._layout, dev = layout, self._dev
         o = np.concatenate([[0], np.cumsum(sizes)])
         cut = lambda i: dev[int(o[i]):int(o[i + 1])]
         self.ids, self.cu_tok, self.past, self.slot, self.seq_of_tok, self.pos_of_tok = (cut(i) for i in range(6))
         self.pages = cut(6).view(n_seq, pages_ld)
         self.rows = cut(7)
         self.paged_tok = cut(8)                                    # tokens of the sequences not in `fresh`
+        at = int(o[-1]) + pad
         self.slot_of_tok = dev[at:at + 2 * n_tok].view(torch.int64)
-        self.n_seq, self.n_tok, self.h2d_bytes = n_seq, n_tok, host.numel() * 4
+
+
+class DecodeGraph:
+    """One captured CUDA graph of the model's step for `n_seq` sequences that each bring one decoded token: the integer
+    description lives in fixed device memory (`StepBatch.refill`), the page table is as wide as the longest request the
+    pool can hold, logits come out for every row.  Replaying it costs one launch instead of one per kernel."""
+
+    def __init__(self, engine, args):
+        self.batch = StepBatch(engine.device, *args, rows=list(range(len(args[1]))), pages_ld=engine.max_pages_per_request)
+        torch.cuda.synchronize(engine.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = engine.model.forward(self.batch, engine.caches)
+        self.first = True
+
+    def run(self, args):
+        if not self.first:
+            self.batch.refill(*args, rows=list(range(len(args[1]))))
+        self.first = False
+        self.graph.replay()
+        return self.logits
 
 
 class Scheduler:
@@ -164,10 +204,12 @@ class Engine:
     """Owns the model's caches and runs steps.  max_tokens: tokens the page pool holds at once (every request rounded up
     to whole pages); max_seqs: state slots, i.e. the most requests alive at once."""
 
-    def __init__(self, model, max_tokens, max_seqs=4, max_step_tokens=2048):
+    def __init__(self, model, max_tokens, max_seqs=4, max_step_tokens=2048, decode_graphs=True):
         self.model, self.device, self.page_size = model, model.device, model.page_size
+        self.decode_graphs, self._graphs, self._decode_seen = decode_graphs, {}, {}
         seq_ops.ensure_host_lib()
         n_pages = -(-int(max_tokens) // self.page_size)
+        self.max_pages_per_request = n_pages
         self.pages = kv_index.KVCacheManager(n_pages + 1, self.page_size, enable_caching=False)      # + the null block
         self.slots = StateSlots(max_seqs)
         self.caches = model.alloc_caches(max_seqs, (n_pages + 1) * self.page_size)
@@ -237,12 +279,37 @@ class Engine:
             w = [n - 1] if want is None else want[e]
             rows += [base + int(i) for i in w]
             base += n
-        batch = StepBatch(self.device, ids, counts, pasts, slots, tables, np.concatenate(slot_map), rows)
-        self.last_batch = batch
-        logits = self.model.forward(batch, self.caches, after_layer=after_layer)     # the caches advance also when no row is asked
+        args = (ids, counts, pasts, slots, tables, np.concatenate(slot_map))
+        logits = self._decode_by_graph(args, rows) if after_layer is None else None
+        if logits is None:
+            batch = StepBatch(self.device, *args, rows=rows)
+            self.last_batch = batch
+            logits = self.model.forward(batch, self.caches, after_layer=after_layer)     # the caches advance also when no row is asked
         for req, n in plan:
             req.n_computed += n
         return logits if rows else None
+
+    def _decode_by_graph(self, args, rows):
+        """Steps in which every request brings exactly one token after its first run as a captured graph, from the
+        second such step of a given batch size on (the first runs eagerly and warms every kernel up)."""
+        counts, pasts = args[1], args[2]
+        n = len(counts)
+        if not self.decode_graphs or any(c != 1 for c in counts) or any(p == 0 for p in pasts):
+            return None
+        if not getattr(self.model, "capturable", lambda n_tok: False)(n):
+            return None
+        g = self._graphs.get(n)
+        if g is None:
+            self._decode_seen[n] = self._decode_seen.get(n, 0) + 1
+            if self._decode_seen[n] < 2:
+                return None
+            try:
+                g = self._graphs[n] = DecodeGraph(self, args)
+            except RuntimeError:             # a step that cannot be captured on this system: stay eager for good
+                self.decode_graphs = False
+                return None
+        out = g.run(args)
+        return out[rows] if rows else out[:0]
 
     def step(self):
         """One scheduler-planned step; returns [(request, new token)] for the requests that produced one."""

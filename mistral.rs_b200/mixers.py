@@ -161,13 +161,16 @@ class RoutedExperts:
         self.top, self.n_groups, self.keep_groups, self.act, self.renorm = top, n_groups, keep_groups, act, renorm
         self.n_experts = w_gate_up.shape[0]
 
+    def streams_weights(self, n_tok):
+        return n_tok * self.top <= self.PAIRS_PER_EXPERT * self.n_experts
+
     def route(self, h):
         logits = F.linear(h.float(), self.w_router)
         return K.moe_route(logits, self.correction, self.n_groups, self.keep_groups, self.top, self.renorm)
 
     def forward(self, h):
         experts, weights = self.route(h)
-        if experts.numel() <= self.PAIRS_PER_EXPERT * self.n_experts:
+        if self.streams_weights(h.shape[0]):
             return K.moe_small(h, self.w_gate_up, self.w_down, experts, weights, self.act)
         counts, order = K.moe_sort(experts, self.n_experts)
         xs = K.moe_gather(h, order, self.top)

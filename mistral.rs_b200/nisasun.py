@@ -163,6 +163,11 @@ class NisasunModel:
     def vocab(self):
         return self.cfg.vocab
 
+    def capturable(self, n_tok):
+        """True when a step of n_tok tokens launches a fixed sequence of kernels with no host read in between (the
+        routed-expert layers then take their weight-streaming path), so it can be captured as a CUDA graph."""
+        return all(lay.mlp is None or not isinstance(lay.mlp, M.RoutedExperts) or lay.mlp.streams_weights(n_tok) for lay in self.layers)
+
     def alloc_caches(self, n_state_slots, n_token_slots):
         return [lay.mixer.alloc_cache(n_state_slots, n_token_slots, self.dtype, self.device) for lay in self.layers]
 

@@ -49,7 +49,12 @@ class ScanArgs(ctypes.Structure):
                 ("decay_tok", ctypes.c_void_p), ("decay_head", ctypes.c_void_p), ("scale_tok", ctypes.c_void_p),
                 ("skip", ctypes.c_void_p), ("state", ctypes.c_void_p),
                 ("cu_tok", ctypes.c_void_p), ("past", ctypes.c_void_p), ("slot", ctypes.c_void_p),
-                ("n_seq", ctypes.c_int), ("n_tok", ctypes.c_int), ("out", ctypes.c_void_p)]
+                ("n_seq", ctypes.c_int), ("n_tok", ctypes.c_int), ("out", ctypes.c_void_p),
+                ("seg_state", ctypes.c_void_p), ("seg_decay", ctypes.c_void_p), ("seg_len", ctypes.c_int), ("n_segs", ctypes.c_int)]
+
+SCAN_SEGMENT = 256                  # tokens per segment when a long portion is scanned as segments side by side
+SCAN_SEGMENT_MIN_TOKENS = 1024      # portions shorter than this run in one pass
+SCAN_SCRATCH_BYTES = 1 << 30
 
 
 def lib():
@@ -159,6 +164,16 @@ def linear_scan(q, q_col, k, k_col, v, v_col, heads, qk_groups, dk, dv, state, b
     a.state = state.data_ptr()
     a.cu_tok, a.past, a.slot = batch.cu_tok.data_ptr(), batch.past.data_ptr(), batch.slot.data_ptr()
     a.n_seq, a.n_tok, a.out = batch.n_seq, T, out.data_ptr()
+    longest = getattr(batch, "longest", 0)
+    if longest >= SCAN_SEGMENT_MIN_TOKENS:
+        seg = SCAN_SEGMENT
+        while batch.n_seq * -(-longest // seg) * heads * dk * dv * 4 > SCAN_SCRATCH_BYTES:
+            seg *= 2
+        n_segs = -(-longest // seg)
+        if n_segs > 1:
+            seg_state = torch.empty(batch.n_seq * n_segs * heads * dk * dv, dtype=torch.float32, device=q.device)
+            seg_decay = torch.empty(batch.n_seq * n_segs * heads, dtype=torch.float32, device=q.device)
+            a.seg_state, a.seg_decay, a.seg_len, a.n_segs = seg_state.data_ptr(), seg_decay.data_ptr(), seg, n_segs
     _ok(lib().mrs_seq_linear_scan(ctypes.byref(a), _st(q)), "linear_scan")
     return out
 

@@ -163,6 +163,21 @@ def test_lightning_mixer(cuda, dtype, tol, portions):
     close_rows(got, want, tol)
 
 
+def test_scan_in_segments(cuda, monkeypatch, full32):
+    """Long portions are scanned as segments side by side (zero-state pass, chaining, output pass): made to happen on
+    short ones here, with ragged last segments, a state carried in from an earlier portion, and a short sequence beside."""
+    monkeypatch.setattr(K, "SCAN_SEGMENT", 16)
+    monkeypatch.setattr(K, "SCAN_SEGMENT_MIN_TOKENS", 40)
+    for layer in (lightning_layer(decay=(0.4, 0.97, 1.0)), parallel_layer(left_scale=0.0, right_scale=1.0)):
+        got, want = mixer_case(cuda, layer, torch.float32, 150, [70, 3, 77])
+        close_rows(got, want, 3e-5)
+    model, prompts, want = full32
+    eng = engine.Engine(model, max_tokens=16 * 14, max_seqs=2)
+    got = replay(eng, prompts, [[("a", 99), ("b", 37)], [("a", 51)]])
+    for name in ("a", "b"):
+        assert_close(got[name], want[name], torch.float32, name)
+
+
 def test_lightning_wide_keys(cuda):
     got, want = mixer_case(cuda, lightning_layer(heads=2, dim=136, vdim=72, decay=(0.9, 0.99)), torch.float32, 40, [13, 1, 26])
     close_rows(got, want, 2e-5)
