@@ -22,7 +22,7 @@ def make_target(directory, product):
     if os.path.exists(product):
         return
     try:
-        subprocess.check_call(["make", "-s", "-C", directory], stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-s", "-j", str(min(8, os.cpu_count() or 1)), "-C", directory], stdout=subprocess.DEVNULL)
     except (OSError, subprocess.CalledProcessError) as e:
         raise ExtensionMissing(f"{product} is missing and `make -C {directory}` failed: {e}") from e
     if not os.path.exists(product):
