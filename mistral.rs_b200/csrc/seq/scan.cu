@@ -17,6 +17,24 @@ namespace seq {
 // shuffles.  Tokens go through in rounds of TC: while one round runs out of f32 shared memory, the next round's
 // q / k / v / a / b stream into a raw staging area (cp.async, 16 bytes at a time when the rows are aligned), and are
 // converted (and activated) between rounds — the global latency hides behind the token loop.
+// two f32 lanes per instruction (sm_100 packed arithmetic): the scan's state update and dot are FMA-issue-bound
+__device__ __forceinline__ uint64_t pack2(float x, float y) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &x, float &y) { asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
@@ -27,7 +45,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 template <typename T, int RK, int TC>
-__global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw, int aligned, int mode) {
+__global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw, int aligned, int mode) {
   // mode 0: the whole portion of a sequence, state from / to its slot.  Long portions are cut into segments of
   // a.seg_len tokens that run side by side: mode 1 advances a ZERO state over one segment and leaves it, with the
   // segment's product of decays, in a.seg_state / a.seg_decay; a small kernel then chains the segments (and the slot's
@@ -54,7 +72,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
   float *state = mode ? a.seg_state + ((int64_t)blockIdx.z * heads + h) * dk * dv : a.state + ((int64_t)a.slot[b] * heads + h) * dk * dv;
   float decay_product = 1.0f;
 
-  float S[RK];
+  uint64_t S[RK / 2];      // the state column's rows as packed pairs (row 2i, row 2i + 1)
   if (mode == 2 || (mode == 0 && a.past[b] > 0)) {   // stage the tile [dk, cw] through shared memory so the global reads run along columns
     float *tile = smem;
     for (int e = threadIdx.x; e < parts * RK * cw; e += nth) {
@@ -63,11 +81,11 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
     }
     __syncthreads();
 #pragma unroll
-    for (int r = 0; r < RK; r++) S[r] = tile[(part * RK + r) * cw + cl];
+    for (int r = 0; r < RK; r += 2) S[r / 2] = pack2(tile[(part * RK + r) * cw + cl], tile[(part * RK + r + 1) * cw + cl]);
     __syncthreads();
   } else {
 #pragma unroll
-    for (int r = 0; r < RK; r++) S[r] = 0.0f;
+    for (int r = 0; r < RK / 2; r++) S[r] = 0ull;
   }
   for (int e = threadIdx.x; e < 2 * TC * dks; e += nth) qs[e] = 0.0f;     // rows past dk stay zero for good
   const float skip = a.skip ? a.skip[h] : 0.0f;
@@ -138,44 +156,53 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
     // four tokens per pass: the state's chain through them is short (two dependent operations per token and row), while
     // their shared-memory reads, dot products and shuffle trees are independent and overlap
     for (int i0 = 0; i0 < n; i0 += 4) {
-      float av[4], bv[4], vv[4], acc[4];
+      float vv[4];
+      uint64_t av2[4], bv2[4], acc2[4];
 #pragma unroll
       for (int u = 0; u < 4; u++) {
         const bool live = i0 + u < n;          // a missing token leaves the state alone (rows past n hold old, finite data)
         vv[u] = vs[(i0 + u) * cw + cl];
-        av[u] = live ? as[i0 + u] : 1.0f;
-        bv[u] = live ? bs[i0 + u] * vv[u] : 0.0f;
-        acc[u] = 0.0f;
-        decay_product *= av[u];
+        const float av = live ? as[i0 + u] : 1.0f, bv = live ? bs[i0 + u] * vv[u] : 0.0f;
+        av2[u] = pack2(av, av);
+        bv2[u] = pack2(bv, bv);
+        acc2[u] = 0ull;
+        decay_product *= av;
       }
 #pragma unroll
       for (int r = 0; r < RK; r += 4) {
-        float4 k4[4], q4[4];
+        ulonglong2 k4[4], q4[4];               // four rows of k / q as two packed pairs
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-          k4[u] = *(const float4 *)(ks + (i0 + u) * dks + part * PS + r);
-          if (mode != 1) q4[u] = *(const float4 *)(qs + (i0 + u) * dks + part * PS + r);
+          k4[u] = *(const ulonglong2 *)(ks + (i0 + u) * dks + part * PS + r);
+          if (mode != 1) q4[u] = *(const ulonglong2 *)(qs + (i0 + u) * dks + part * PS + r);
         }
-        float s0 = S[r], s1 = S[r + 1], s2 = S[r + 2], s3 = S[r + 3];
+        uint64_t s01 = S[r / 2], s23 = S[r / 2 + 1];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-          s0 = fmaf(k4[u].x, bv[u], av[u] * s0);
-          s1 = fmaf(k4[u].y, bv[u], av[u] * s1);
-          s2 = fmaf(k4[u].z, bv[u], av[u] * s2);
-          s3 = fmaf(k4[u].w, bv[u], av[u] * s3);
-          if (mode != 1) acc[u] = fmaf(s0, q4[u].x, fmaf(s1, q4[u].y, fmaf(s2, q4[u].z, fmaf(s3, q4[u].w, acc[u]))));
+          s01 = fma2(k4[u].x, bv2[u], mul2(av2[u], s01));
+          s23 = fma2(k4[u].y, bv2[u], mul2(av2[u], s23));
+          if (mode != 1) acc2[u] = fma2(s01, q4[u].x, fma2(s23, q4[u].y, acc2[u]));
         }
-        S[r] = s0; S[r + 1] = s1; S[r + 2] = s2; S[r + 3] = s3;
+        S[r / 2] = s01;
+        S[r / 2 + 1] = s23;
       }
-      if (mode != 1)
+      if (mode != 1) {
+        float acc[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          float lo, hi;
+          unpack2(acc2[u], lo, hi);
+          acc[u] = lo + hi;
+        }
         for (int m = 1; m < parts; m <<= 1) {
 #pragma unroll
           for (int u = 0; u < 4; u++) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
         }
-      if (part == 0 && mode != 1) {
+        if (part == 0) {
 #pragma unroll
-        for (int u = 0; u < 4; u++)
-          if (i0 + u < n) os[(i0 + u) * cw + cl] = fmaf(skip, vv[u], acc[u]);
+          for (int u = 0; u < 4; u++)
+            if (i0 + u < n) os[(i0 + u) * cw + cl] = fmaf(skip, vv[u], acc[u]);
+        }
       }
     }
     __syncthreads();
@@ -190,7 +217,12 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(const mrs_seq_scan_arg
   if (mode != 2) {   // the state goes back the way it came
     float *tile = smem;
 #pragma unroll
-    for (int r = 0; r < RK; r++) tile[(part * RK + r) * cw + cl] = S[r];
+    for (int r = 0; r < RK; r += 2) {
+      float lo, hi;
+      unpack2(S[r / 2], lo, hi);
+      tile[(part * RK + r) * cw + cl] = lo;
+      tile[(part * RK + r + 1) * cw + cl] = hi;
+    }
     __syncthreads();
     for (int e = threadIdx.x; e < parts * RK * cw; e += nth) {
       const int r = e / cw, c = e % cw;

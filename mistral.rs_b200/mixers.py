@@ -154,7 +154,9 @@ class RoutedExperts:
     (token, expert) pairs: two weight-streaming kernels.  Many: rows sorted by expert, one GEMM pair per expert that
     has rows (the per-expert row counts cross to the host once per layer), weighted combine in f32."""
 
-    PAIRS_PER_EXPERT = 2       # up to this many (token, expert) pairs per expert the weights are simply streamed per pair
+    # Up to this many (token, expert) pairs per expert the weights are simply streamed once per pair: 4 while an expert is
+    # small enough that repeated reads hit L2, 2 above that.
+    SMALL_EXPERT_BYTES = 32 << 20
 
     def __init__(self, w_router, correction, w_gate_up, w_down, top, n_groups, keep_groups, act, renorm=False):
         self.w_router, self.correction, self.w_gate_up, self.w_down = w_router, correction, w_gate_up, w_down
@@ -162,7 +164,9 @@ class RoutedExperts:
         self.n_experts = w_gate_up.shape[0]
 
     def streams_weights(self, n_tok):
-        return n_tok * self.top <= self.PAIRS_PER_EXPERT * self.n_experts
+        expert_bytes = (self.w_gate_up[0].numel() + self.w_down[0].numel()) * self.w_down.element_size()
+        per_expert = 4 if expert_bytes <= self.SMALL_EXPERT_BYTES else 2
+        return n_tok * self.top <= per_expert * self.n_experts
 
     def route(self, h):
         logits = F.linear(h.float(), self.w_router)

@@ -106,9 +106,10 @@ def one_seq_batch(device, n, past=0, slot=0, page_size=16, first_page=1):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_streams_read_write_norm(cuda, dtype):
+@pytest.mark.parametrize("S,W", [(3, 50), (1, 64), (2, 136), (4, 24), (6, 40), (11, 9)])
+def test_streams_read_write_norm(cuda, dtype, S, W):
     g = torch.Generator().manual_seed(1)
-    T, S, W = 9, 3, 50
+    T = 9
     xs = torch.randn(T, S, W, generator=g)
     w_in, w_out, w_mix, nw, nw2 = torch.randn(S, generator=g), torch.randn(S, generator=g), torch.randn(S, S, generator=g), 0.2 * torch.randn(W, generator=g), 0.2 * torch.randn(W, generator=g)
     y = torch.randn(T, W, generator=g).to(dtype)
