@@ -41,6 +41,7 @@ class Request:
     generated: list = field(default_factory=list)
     finished: bool = False
     admitted: bool = False
+    slot: int = -1                       # state slot once admitted
 
 
 class StateSlots:
@@ -87,14 +88,6 @@ class StepBatch:
         self._host, self._dev = host, host.to(device, non_blocking=True)
         self._bind(layout)
 
-    def refill(self, ids, counts, pasts, slots, tables, slot_of_tok, rows):
-        """The same shapes with new contents, into the same device memory (a captured graph reads it in place)."""
-        host, layout = self._pack(ids, counts, pasts, slots, tables, slot_of_tok, rows)
-        if host.numel() != self._dev.numel() or layout != self._layout:
-            raise ValueError("refill needs the sizes the batch was made with")
-        self._host = host
-        self._dev.copy_(host, non_blocking=True)
-
     def _pack(self, ids, counts, pasts, slots, tables, slot_of_tok, rows):
         n_seq, n_tok = len(counts), int(sum(counts))
         pages_ld = self._pages_ld or max(1, max(len(t) for t in tables))
@@ -139,22 +132,41 @@ class StepBatch:
 
 
 class DecodeGraph:
-    """One captured CUDA graph of the model's step for `n_seq` sequences that each bring one decoded token: the integer
-    description lives in fixed device memory (`StepBatch.refill`), the page table is as wide as the longest request the
-    pool can hold, logits come out for every row.  Replaying it costs one launch instead of one per kernel."""
+    """One captured CUDA graph of the model's step for `n` sequences that each bring one decoded token.  The integer
+    description lives in fixed device memory and is staged in one fixed pinned buffer: token ids, positions and state
+    slots are written as arrays, block tables and cache slots by the KV manager's batched `decode_step` (one native
+    call for the whole batch, straight into the staging memory); then one copy and one graph launch.  The page table
+    is as wide as the longest request the pool can hold; logits come out for every row."""
 
-    def __init__(self, engine, args):
-        self.batch = StepBatch(engine.device, *args, rows=list(range(len(args[1]))), pages_ld=engine.max_pages_per_request)
+    def __init__(self, engine, n):
+        self.engine, self.n, P = engine, n, engine.max_pages_per_request
+        shape = ([0] * n, [1] * n, [1] * n, [0] * n, [[0]] * n, np.zeros(n, dtype=np.int64))
+        self.batch = StepBatch(engine.device, *shape, rows=list(range(n)), pages_ld=P)
+        sizes, pad = self.batch._layout[0], self.batch._layout[1]
+        self.host = self.batch._host                       # pinned; the constant parts (offsets, row lists) stay as packed
+        hv, o = self.host.numpy(), np.concatenate([[0], np.cumsum(sizes)])
+        self.h_ids, self.h_past, self.h_slot, self.h_pos = hv[o[0]:o[1]], hv[o[2]:o[3]], hv[o[3]:o[4]], hv[o[5]:o[6]]
+        self.h_pages = hv[o[6]:o[7]].reshape(n, P)
+        at = int(o[-1]) + pad
+        self.h_slot_of_tok = hv[at:at + 2 * n].view(np.int64)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
         torch.cuda.synchronize(engine.device)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.logits = engine.model.forward(self.batch, engine.caches)
-        self.first = True
 
-    def run(self, args):
-        if not self.first:
-            self.batch.refill(*args, rows=list(range(len(args[1]))))
-        self.first = False
+    def run(self, reqs):
+        self.copied.synchronize()                          # the staging memory is free again
+        pasts = [r.n_computed for r in reqs]
+        self.h_ids[:] = [r.tokens[r.n_computed] for r in reqs]
+        self.h_past[:] = pasts
+        self.h_pos[:] = pasts
+        self.h_slot[:] = [r.slot for r in reqs]
+        self.engine.pages.decode_step([r.rid for r in reqs], [p + 1 for p in pasts], self.h_pages.shape[1], tables=self.h_pages,
+                                      slots=self.h_slot_of_tok)
+        self.batch._dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
         self.graph.replay()
         return self.logits
 
@@ -247,7 +259,7 @@ class Engine:
 
     def finish(self, req):
         """Give back the request's pages and state slot."""
-        req.finished = True
+        req.finished, req.slot = True, -1
         self.pages.free(req.rid)
         self.slots.release(req.rid)
         self.scheduler.retire(req)
@@ -259,6 +271,10 @@ class Engine:
         """plan: [(request, n_new)] — the next n_new tokens of request.tokens past n_computed.  want: per entry the
         offsets inside its portion whose logits are asked for (default: the last one).  Returns f32 logits
         [asked rows, vocab] in plan order, or None when nothing is asked."""
+        if after_layer is None and self.decode_graphs and all(n == 1 and r.n_computed > 0 and r.slot >= 0 for r, n in plan):
+            out = self._decode_by_graph(plan, want)
+            if out is not NotImplemented:
+                return out
         ids, counts, pasts, slots, tables, slot_map, rows = [], [], [], [], [], [], []
         base = 0
         for e, (req, n) in enumerate(plan):
@@ -269,7 +285,7 @@ class Engine:
                 raise MemoryError("no state slot is free")
             if self.pages.allocate_slots(req.rid, req.n_computed + n) is None:
                 raise MemoryError("the page pool cannot hold this step")
-            req.admitted = True
+            req.admitted, req.slot = True, slot
             ids += req.tokens[req.n_computed:req.n_computed + n]
             counts.append(n)
             pasts.append(req.n_computed)
@@ -279,37 +295,38 @@ class Engine:
             w = [n - 1] if want is None else want[e]
             rows += [base + int(i) for i in w]
             base += n
-        args = (ids, counts, pasts, slots, tables, np.concatenate(slot_map))
-        logits = self._decode_by_graph(args, rows) if after_layer is None else None
-        if logits is None:
-            batch = StepBatch(self.device, *args, rows=rows)
-            self.last_batch = batch
-            logits = self.model.forward(batch, self.caches, after_layer=after_layer)     # the caches advance also when no row is asked
+        batch = StepBatch(self.device, ids, counts, pasts, slots, tables, np.concatenate(slot_map), rows)
+        self.last_batch = batch
+        logits = self.model.forward(batch, self.caches, after_layer=after_layer)     # the caches advance also when no row is asked
         for req, n in plan:
             req.n_computed += n
         return logits if rows else None
 
-    def _decode_by_graph(self, args, rows):
+    def _decode_by_graph(self, plan, want):
         """Steps in which every request brings exactly one token after its first run as a captured graph, from the
         second such step of a given batch size on (the first runs eagerly and warms every kernel up)."""
-        counts, pasts = args[1], args[2]
-        n = len(counts)
-        if not self.decode_graphs or any(c != 1 for c in counts) or any(p == 0 for p in pasts):
-            return None
+        n = len(plan)
+        if any(req.n_computed + 1 > len(req.tokens) for req, _ in plan):
+            raise ValueError("a step entry must bring 1..remaining tokens of its request")
         if not getattr(self.model, "capturable", lambda n_tok: False)(n):
-            return None
+            return NotImplemented
         g = self._graphs.get(n)
         if g is None:
             self._decode_seen[n] = self._decode_seen.get(n, 0) + 1
             if self._decode_seen[n] < 2:
-                return None
+                return NotImplemented
             try:
-                g = self._graphs[n] = DecodeGraph(self, args)
+                g = self._graphs[n] = DecodeGraph(self, n)
             except RuntimeError:             # a step that cannot be captured on this system: stay eager for good
                 self.decode_graphs = False
-                return None
-        out = g.run(args)
-        return out[rows] if rows else out[:0]
+                return NotImplemented
+        out = g.run([req for req, _ in plan])
+        rows = list(range(n)) if want is None else [e for e, w in enumerate(want) if len(w)]
+        for req, _ in plan:
+            req.n_computed += 1
+        if not rows:
+            return None
+        return out.clone() if len(rows) == n else out[rows]
 
     def step(self):
         """One scheduler-planned step; returns [(request, new token)] for the requests that produced one."""
