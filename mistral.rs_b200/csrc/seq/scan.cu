@@ -344,28 +344,56 @@ __global__ void ssm_steps_kernel(const T *__restrict__ in, int64_t in_ld, int co
 }
 
 // ---- gated group RMS norm ------------------------------------------------------------------------------------------
-// one CTA per (token, group)
-template <typename T>
-__global__ void gated_group_norm_kernel(const float *__restrict__ x, const T *__restrict__ gate, int64_t gate_ld,
+// one CTA per (token, group); VEC = 4: four columns per thread and pass, the row kept in registers between the passes
+// when it fits (KEEP vector items per thread), so a short batch pays one round of global latency, not sixteen
+template <typename T, int VEC, int KEEP>
+__global__ void __launch_bounds__(1024) gated_group_norm_kernel(const float *__restrict__ x, const T *__restrict__ gate, int64_t gate_ld,
                                         const float *__restrict__ weight, T *__restrict__ out, int64_t out_ld, float out_scale, int cols,
                                         int groups, float eps, int gate_act, int gate_first) {
   __shared__ float red[33];
   const int t = blockIdx.x, gr = blockIdx.y, n = cols / groups, c0 = gr * n;
   const float *xr = x + (int64_t)t * cols + c0;
   const T *gp = gate ? gate + (int64_t)t * gate_ld + c0 : nullptr;
+  T *dst = out + (int64_t)t * out_ld + c0;
+  const float *w = weight + c0;
   float ss = 0.0f;
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    float v = xr[c];
-    if (gp && gate_first) v *= apply_act(to_f32<T>(gp[c]), gate_act);
-    ss = fmaf(v, v, ss);
-  }
-  const float inv = rsqrtf_exact(block_sum(ss, red) / (float)n + eps);
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    float v = xr[c];
-    const float gv = gp ? apply_act(to_f32<T>(gp[c]), gate_act) : 1.0f;
-    if (gate_first) v = v * gv * inv * weight[c0 + c];
-    else v = v * inv * weight[c0 + c] * gv;
-    out[(int64_t)t * out_ld + c0 + c] = from_f32<T>(v * out_scale);
+  if (VEC == 4) {
+    float4 xv[KEEP], gv[KEEP];
+#pragma unroll
+    for (int it = 0; it < KEEP; it++) {
+      const int c = (it * blockDim.x + threadIdx.x) * 4;
+      if (c < n) {
+        xv[it] = *(const float4 *)(xr + c);
+        gv[it] = gp ? act4(load4<T>(gp + c), gate_act) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (gate_first) xv[it] = make_float4(xv[it].x * gv[it].x, xv[it].y * gv[it].y, xv[it].z * gv[it].z, xv[it].w * gv[it].w);
+        ss += xv[it].x * xv[it].x + xv[it].y * xv[it].y + xv[it].z * xv[it].z + xv[it].w * xv[it].w;
+      }
+    }
+    const float inv = rsqrtf_exact(block_sum(ss, red) / (float)n + eps);
+#pragma unroll
+    for (int it = 0; it < KEEP; it++) {
+      const int c = (it * blockDim.x + threadIdx.x) * 4;
+      if (c < n) {
+        const float4 ww = *(const float4 *)(w + c);
+        float4 r = make_float4(xv[it].x * inv * ww.x, xv[it].y * inv * ww.y, xv[it].z * inv * ww.z, xv[it].w * inv * ww.w);
+        if (!gate_first) r = make_float4(r.x * gv[it].x, r.y * gv[it].y, r.z * gv[it].z, r.w * gv[it].w);
+        store4<T>(dst + c, make_float4(r.x * out_scale, r.y * out_scale, r.z * out_scale, r.w * out_scale));
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      float v = xr[c];
+      if (gp && gate_first) v *= apply_act(to_f32<T>(gp[c]), gate_act);
+      ss = fmaf(v, v, ss);
+    }
+    const float inv = rsqrtf_exact(block_sum(ss, red) / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      float v = xr[c];
+      const float gv = gp ? apply_act(to_f32<T>(gp[c]), gate_act) : 1.0f;
+      if (gate_first) v = v * gv * inv * w[c];
+      else v = v * inv * w[c] * gv;
+      dst[c] = from_f32<T>(v * out_scale);
+    }
   }
 }
 
@@ -445,8 +473,21 @@ extern "C" int mrs_seq_gated_group_norm(const float *x, const void *gate, int64_
                                         int gate_first, int64_t stream) {
   if (n_tok <= 0) return 0;
   if (groups < 1 || cols % groups) return -2;
-  const int n = cols / groups, th = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
-  SEQ_DISPATCH_DTYPE(dtype, (gated_group_norm_kernel<T><<<dim3(n_tok, groups), th, 0, (cudaStream_t)stream>>>(
+  const int n = cols / groups;
+  const bool vec = n % 4 == 0 && gate_ld % 4 == 0 && out_ld % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)gate % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0 && (uintptr_t)weight % 16 == 0 && n <= 4 * 1024 * 4;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (vec) {
+    const int items = n / 4;                                    // vector items per row
+    int th = 64;
+    while (th < 1024 && th * 4 < items) th *= 2;               // up to four items per thread, up to 1024 threads
+    if (n_tok <= 64) while (th < 1024 && th < items) th *= 2;   // short batches: one item per thread where possible
+    SEQ_DISPATCH_DTYPE(dtype, (gated_group_norm_kernel<T, 4, 4><<<dim3(n_tok, groups), th, 0, st>>>(
+                                  x, (const T *)gate, gate_ld, weight, (T *)out, out_ld, out_scale, cols, groups, eps, gate_act, gate_first)));
+    return launch_status();
+  }
+  const int th = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+  SEQ_DISPATCH_DTYPE(dtype, (gated_group_norm_kernel<T, 1, 1><<<dim3(n_tok, groups), th, 0, st>>>(
                                 x, (const T *)gate, gate_ld, weight, (T *)out, out_ld, out_scale, cols, groups, eps, gate_act, gate_first)));
   return launch_status();
 }

@@ -28,7 +28,7 @@ template <int NS> struct StreamCount {
 
 // u = sum_s w_in[s] x_s ; out = u / sqrt(mean(u^2) + eps) * (unit_offset + w)
 template <typename T, int NS>
-__global__ void streams_read_norm_kernel(const float *__restrict__ streams, const float *__restrict__ w_in,
+__global__ void __launch_bounds__(1024) streams_read_norm_kernel(const float *__restrict__ streams, const float *__restrict__ w_in,
                                          const float *__restrict__ norm_w, float eps, float unit_offset,
                                          const int32_t *__restrict__ rows, T *__restrict__ out, int n_streams, int width) {
   __shared__ float red[33];
@@ -60,7 +60,7 @@ __global__ void streams_read_norm_kernel(const float *__restrict__ streams, cons
 // x_r <- sum_s mix[s][r] x_s + w_out[r] y, every r from the old x; then (optionally) the next read + norm.
 // VEC = 4: four neighbouring columns per thread (16-byte stream accesses) when the width allows; VEC = 1 otherwise.
 template <typename T, int VEC, int NS>
-__global__ void streams_write_kernel(float *__restrict__ streams, const float *__restrict__ w_mix, const float *__restrict__ w_out,
+__global__ void __launch_bounds__(1024) streams_write_kernel(float *__restrict__ streams, const float *__restrict__ w_mix, const float *__restrict__ w_out,
                                      const T *__restrict__ y, int n_streams, int width, const float *__restrict__ next_in,
                                      const float *__restrict__ next_norm_w, float eps, float unit_offset, T *__restrict__ next_out) {
   constexpr int CAP = StreamCount<NS>::CAP;
@@ -129,7 +129,10 @@ __global__ void streams_write_kernel(float *__restrict__ streams, const float *_
   }
 }
 
-static int threads_for(int width) { return width >= 1024 ? 256 : (width >= 256 ? 128 : 64); }
+static int threads_for(int width, int n_rows = 1 << 30) {
+  if (n_rows <= 64) return width >= 1024 ? 1024 : (width >= 512 ? 512 : (width >= 256 ? 256 : (width >= 128 ? 128 : 64)));   // short batches: latency, not occupancy
+  return width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+}
 
 }  // namespace seq
 
@@ -149,7 +152,7 @@ extern "C" int mrs_seq_streams_read_norm(const float *streams, const float *w_in
                                          int64_t stream) {
   if (n_rows <= 0) return 0;
   if (n_streams < 1 || n_streams > MAX_STREAMS) return -2;
-#define SEQ_READ(NS) streams_read_norm_kernel<T, NS><<<n_rows, threads_for(width), 0, (cudaStream_t)stream>>>( \
+#define SEQ_READ(NS) streams_read_norm_kernel<T, NS><<<n_rows, threads_for(width, n_rows), 0, (cudaStream_t)stream>>>( \
       streams, w_in, norm_w, eps, unit_offset, rows, (T *)out, n_streams, width)
   SEQ_DISPATCH_DTYPE(dtype, {
     switch (n_streams) {
@@ -171,7 +174,11 @@ extern "C" int mrs_seq_streams_write(float *streams, const float *w_mix, const f
   if (n_streams < 1 || n_streams > MAX_STREAMS) return -2;
   const bool vec = width % 4 == 0 && (uintptr_t)streams % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)next_out % 16 == 0 &&
                    (uintptr_t)next_norm_w % 16 == 0;
-  const int th = vec ? (width >= 4096 ? 256 : (width >= 512 ? 128 : 64)) : threads_for(width);
+  int th = vec ? (width >= 4096 ? 256 : (width >= 512 ? 128 : 64)) : threads_for(width);
+  if (n_tok <= 64) {   // short batches: one vector item per thread where possible
+    const int items = vec ? width / 4 : width;
+    while (th < 1024 && th < items) th *= 2;
+  }
 #define SEQ_WRITE(V, NS) streams_write_kernel<T, V, NS><<<n_tok, th, 0, (cudaStream_t)stream>>>( \
       streams, w_mix, w_out, (const T *)y, n_streams, width, next_in, next_norm_w, eps, unit_offset, (T *)next_out)
   SEQ_DISPATCH_DTYPE(dtype, {

@@ -150,16 +150,28 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
 #pragma unroll
     for (int c = 0; c < VPAIRS; c++) { acc[c].x *= corr; acc[c].y *= corr; }
     const int n = min(32, pos - j0 + 1);
-    for (int i = 0; i < n; i++) {
-      const float pi = __shfl_sync(0xffffffffu, p, i);
-      const int64_t si = __shfl_sync(0xffffffffu, slot, i);
-      const T *vr = v_cache + (si * kv_heads + g) * dv;
+    // eight keys per pass: their value rows are fetched together, so the loads overlap instead of queueing behind the
+    // shuffles that carry each key's slot
+    for (int i0 = 0; i0 < n; i0 += 8) {
+      float pi[8];
+      float2 vv[8][VPAIRS];
 #pragma unroll
-      for (int c = 0; c < VPAIRS; c++)
-        if (c * 64 + 2 * lane < dv) {
-          const float2 vv = load2<T>(vr + c * 64 + 2 * lane);
-          acc[c].x = fmaf(pi, vv.x, acc[c].x);
-          acc[c].y = fmaf(pi, vv.y, acc[c].y);
+      for (int u = 0; u < 8; u++) {
+        const int i = min(i0 + u, 31);
+        const float pu = __shfl_sync(0xffffffffu, p, i);
+        pi[u] = i0 + u < n ? pu : 0.0f;
+        const int64_t si = __shfl_sync(0xffffffffu, slot, i);
+        const T *vr = v_cache + (si * kv_heads + g) * dv;          // a lane past n carries slot 0: a valid row, weight 0
+#pragma unroll
+        for (int c = 0; c < VPAIRS; c++)
+          vv[u][c] = c * 64 + 2 * lane < dv ? load2<T>(vr + c * 64 + 2 * lane) : make_float2(0.0f, 0.0f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++)
+#pragma unroll
+        for (int c = 0; c < VPAIRS; c++) {
+          acc[c].x = fmaf(pi[u], vv[u][c].x, acc[c].x);
+          acc[c].y = fmaf(pi[u], vv[u][c].y, acc[c].y);
         }
     }
     m = m_new;
