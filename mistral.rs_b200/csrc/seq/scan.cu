@@ -75,9 +75,20 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
   uint64_t S[RK / 2];      // the state column's rows as packed pairs (row 2i, row 2i + 1)
   if (mode == 2 || (mode == 0 && a.past[b] > 0)) {   // stage the tile [dk, cw] through shared memory so the global reads run along columns
     float *tile = smem;
-    for (int e = threadIdx.x; e < parts * RK * cw; e += nth) {
-      const int r = e / cw, c = e % cw;
-      tile[e] = (r < dk && col0 + c < dv) ? state[(int64_t)r * dv + col0 + c] : 0.0f;
+    if (dv % 4 == 0 && cw % 4 == 0 && ((uintptr_t)state & 15) == 0) {   // all 16-byte pieces in flight at once
+      const int per = cw / 4;
+      for (int e = threadIdx.x; e < parts * RK * per; e += nth) {
+        const int r = e / per, c = (e % per) * 4;
+        if (r < dk && col0 + c < dv) cp_async16(tile + r * cw + c, state + (int64_t)r * dv + col0 + c);
+        else *(float4 *)(tile + r * cw + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+      cp_async_commit();
+      cp_async_wait_all();
+    } else {
+      for (int e = threadIdx.x; e < parts * RK * cw; e += nth) {
+        const int r = e / cw, c = e % cw;
+        tile[e] = (r < dk && col0 + c < dv) ? state[(int64_t)r * dv + col0 + c] : 0.0f;
+      }
     }
     __syncthreads();
 #pragma unroll

@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
       const T *kr = k_cache + (slot * kv_heads + g) * dk;
       float a0 = 0.0f, a1 = 0.0f;
       int d = 0;
+#pragma unroll 4
       for (; d + 2 * N <= dk; d += 2 * N) {
         a0 += dot16<T>(qv + d, kr + d);
         a1 += dot16<T>(qv + d + N, kr + d + N);
