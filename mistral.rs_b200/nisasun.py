@@ -53,7 +53,7 @@ class NisasunConfig:
                             p + "mix.o": (W, H * dv), p + "mix.norm": (H * dv,)})
             else:
                 a, r = m["left"], m["right"]
-                H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+                H, G, dk, dv = a["heads"], a.get("kv_heads", a["heads"]), a["dim"], a["vdim"]
                 out.update({p + "mix.left.q": (H * dk, W), p + "mix.left.k": (G * dk, W), p + "mix.left.v": (G * dv, W),
                             p + "mix.left.q.norm": (dk,), p + "mix.left.k.norm": (dk,), p + "mix.left.o": (W, H * dv)})
                 inner, gn = r["heads"] * r["vdim"], r["groups"] * r["state"]
@@ -116,14 +116,16 @@ class NisasunModel:
             lay.norm1 = vec(p + "norm1")
             lay.hc1 = M.StreamResidual(vec(p + "hc1.in"), vec(p + "hc1.out"), vec(p + "hc1.mix"))
             if L["type"] == "lightning":
-                decay = torch.tensor([float(d) for d in m["decay"]], dtype=torch.float32, device=device)
+                per_head = m["decay"] if isinstance(m["decay"], (list, tuple)) else [m["decay"]] * m["heads"]   # one value: every head
+                decay = torch.tensor([float(d) for d in per_head], dtype=torch.float32, device=device)
                 if decay.numel() != m["heads"]:
                     raise ValueError(f"layer {i}: one decay per head is needed")
                 lay.mixer = M.LinearAttentionMixer(mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g"), mat(p + "mix.o"),
                                                    vec(p + "mix.norm"), decay, m["heads"], m["dim"], m["vdim"], cfg.eps)
             else:
                 a, r = m["left"], m["right"]
-                attn = M.WindowAttention(a["heads"], a["kv_heads"], a["dim"], a["vdim"], float(a["scale"]), int(a["mask"]["size"]),
+                attn = M.WindowAttention(a["heads"], a.get("kv_heads", a["heads"]), a["dim"], a["vdim"], float(a["scale"]),
+                                         int((a.get("mask") or {}).get("size", 0)),      # no mask entry: every earlier position
                                          vec(p + "mix.left.q.norm"), vec(p + "mix.left.k.norm"), cfg.eps)
                 ssm = M.StateSpaceMixer(r["heads"], r["vdim"], r["state"], r["groups"], r["norm_groups"], vec(p + "mix.right.conv"),
                                         vec(p + "mix.right.conv.b"), vec(p + "mix.right.dt_bias"), vec(p + "mix.right.A_log"),
@@ -145,8 +147,9 @@ class NisasunModel:
                     E = r["experts"]
                     gu = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(E)]).contiguous()
                     dn = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(E)]).contiguous()
-                    lay.mlp = M.RoutedExperts(vec(p + "mlp.router"), vec(p + "mlp.correction"), gu, dn, r["top"], r["groups"]["count"],
-                                              r["groups"]["keep"], K.ACT_SILU)
+                    grp = r.get("groups") or {"count": 1, "keep": 1}                      # no grouping: one group, kept
+                    lay.mlp = M.RoutedExperts(vec(p + "mlp.router"), vec(p + "mlp.correction"), gu, dn, r["top"], grp["count"], grp["keep"],
+                                              K.ACT_SILU)
             self.layers.append(lay)
 
     # ---- loading ------------------------------------------------------------------------------------
