@@ -19,7 +19,8 @@ extern "C" {
 #endif
 
 enum { MRS_SEQ_BF16 = 1, MRS_SEQ_F32 = 2 };
-enum { MRS_SEQ_ACT_NONE = 0, MRS_SEQ_ACT_SILU = 1, MRS_SEQ_ACT_GELU_TANH = 2, MRS_SEQ_ACT_SIGMOID = 3 };
+enum { MRS_SEQ_ACT_NONE = 0, MRS_SEQ_ACT_SILU = 1, MRS_SEQ_ACT_GELU_TANH = 2, MRS_SEQ_ACT_SIGMOID = 3, MRS_SEQ_ACT_GELU_ERF = 4,
+       MRS_SEQ_ACT_RELU_SQ = 5 };
 
 /* ---- residual streams ------------------------------------------------------------------------------ */
 /* streams[t][s][:] = table[ids[t]][:] for every stream s (streams f32 [n_tok, n_streams, width]). */
@@ -35,6 +36,19 @@ int mrs_seq_streams_read_norm(const float *streams, const float *w_in, const flo
 int mrs_seq_streams_write(float *streams, const float *w_mix, const float *w_out, const void *y, int dtype, int n_tok,
                           int n_streams, int width, const float *next_in, const float *next_norm_w, float eps,
                           float unit_offset, void *next_out, int64_t stream);
+
+/* ---- single residual with Dynamic Tanh norms -------------------------------------------------------- */
+/* A norm without statistics: dyt(z)[c] = tanh(alpha * z[c]) * weight[c] + bias[c]; alpha is ONE f32 on the device.
+ * out[r] = dyt(x[row(r)]) for the f32 residual x [n_tok, width]; rows NULL: all tokens in order. */
+int mrs_seq_tanh_norm_rows(const float *x, const int32_t *rows, const float *alpha, const float *weight, const float *bias,
+                           void *out, int dtype, int n_rows, int width, int64_t stream);
+/* One pass over the residual, every part optional (NULL: skipped), in this order:
+ *   x <- x + dyt_post(y)        (y: a sublayer's output, activation type)
+ *   x <- x + extra              (extra f32 [n_tok, width])
+ *   next_out <- dyt_next(x)     (the next sublayer's input, activation type) */
+int mrs_seq_residual_tanh_norm(float *x, const void *y, int dtype, const float *post_alpha, const float *post_weight,
+                               const float *post_bias, const float *extra, const float *next_alpha, const float *next_weight,
+                               const float *next_bias, void *next_out, int n_tok, int width, int64_t stream);
 
 /* ---- elementwise / norms --------------------------------------------------------------------------- */
 /* x[t][c] = act(x[t][c]) in place for c < cols (row stride ld) */
@@ -86,6 +100,26 @@ typedef struct {
 } mrs_seq_scan_args;
 int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream);
 
+/* ---- stabilised matrix memory (mLSTM) ---------------------------------------------------------------- */
+/* Gates of a matrix memory with a running maximum, per token t and head h, from raw gate pre-activations
+ * raw_in / raw_forget f32 [n_tok, heads] (row stride raw_ld) that already hold their biases:
+ *   i = cap tanh(raw_in / cap), f = logsigmoid(cap tanh(raw_forget / cap))   (cap <= 0: no soft cap)
+ *   m_t = max(f + m_(t-1), i);  keep[t][h] = exp(f + m_(t-1) - m_t);  take[t][h] = exp(i - m_t);  m_tok[t][h] = m_t
+ * m is carried per sequence in m_state f32 [n_slots, heads] and starts at 0 when past == 0.  keep / take are the
+ * decay_tok / scale_tok of mrs_seq_linear_scan. */
+int mrs_seq_mlstm_gates(const float *raw_in, const float *raw_forget, int64_t raw_ld, float cap, int heads, float *m_state,
+                        const int32_t *cu_tok, const int32_t *past, const int32_t *slot, int n_seq, int n_tok, float *keep,
+                        float *take, float *m_tok, int64_t stream);
+/* vaug[t][h][0:dv] = v[t][h][:], vaug[t][h][dv] = 1, vaug[t][h][dv+1:dvp] = 0: with these values the scan's column dv
+ * carries the normaliser n_t = keep n_(t-1) + take k_t and its output column dv is n_t . q_t. */
+int mrs_seq_append_ones(const void *v, int64_t v_ld, int dtype, int heads, int dv, int dvp, int n_tok, void *vaug, int64_t stream);
+/* o f32 [n_tok, heads, dvp] from the scan over augmented values: per head
+ *   y = q_scale o[0:dv] / (max(|q_scale o[dv]|, exp(-m_tok)) + 1e-6);  y <- y / rms(y) (eps) * weight[h][:] * sigmoid(gate[h][:])
+ * gate: activation type, row stride gate_ld; out: activation type [n_tok, heads * dv] with row stride out_ld. */
+int mrs_seq_mlstm_out_norm(const float *o, int dvp, const float *m_tok, float q_scale, const void *gate, int64_t gate_ld,
+                           const float *weight, float eps, int heads, int dv, void *out, int64_t out_ld, int dtype, int n_tok,
+                           int64_t stream);
+
 /* ---- windowed attention over a paged cache --------------------------------------------------------- */
 /* Per-head RMS norm of q and k (both in place) with weights shared by the heads (NULL: no norm), then k and v of the new
  * tokens go to their cache slots.  Cache: k_cache [n_slots, kv_heads, dk], v_cache [n_slots, kv_heads, dv]
@@ -100,6 +134,57 @@ int mrs_seq_window_attention(const void *q, int64_t q_ld, const void *k_cache, c
                              int kv_heads, int dk, int dv, float scale, int window, const int32_t *pages, int pages_ld,
                              int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, const int32_t *tok_index,
                              int n_tok, void *out, int64_t out_ld, float out_scale, int64_t stream);
+/* The general forms of the two calls above.
+ * prepare: norm_mode 0 none, 1 per head (weights [dk], shared by the heads), 2 over the whole projection at once
+ * (weights [heads * dk] and [kv_heads * dk]); then rotation of the first rot_dims entries of every q / k head in pairs
+ * (i, i + rot_dims / 2) by cos_sin f32 [n_tok, rot_dims / 2, 2] (NULL: none); q and k change in place, k and v go to their
+ * cache slots.  v NULL: the values are the keys as projected (before norm and rotation; needs dv == dk); v_copy, when
+ * given, also receives those values ([n_tok, kv_heads, dk] with row stride v_copy_ld) for a kernel that reads fresh rows. */
+enum { MRS_SEQ_QK_NORM_NONE = 0, MRS_SEQ_QK_NORM_HEAD = 1, MRS_SEQ_QK_NORM_WHOLE = 2 };
+typedef struct {
+  void *q, *k;
+  const void *v;
+  void *v_copy;
+  int64_t q_ld, k_ld, v_ld, v_copy_ld;
+  int dtype, norm_mode;
+  const float *q_norm_w, *k_norm_w;
+  float eps;
+  int heads, kv_heads, dk, dv;
+  int rot_dims;
+  const float *cos_sin;
+  void *k_cache, *v_cache;
+  const int64_t *slot_of_tok;
+  int n_tok;
+} mrs_seq_attn_prepare_args;
+int mrs_seq_attention_prepare(const mrs_seq_attn_prepare_args *args, int64_t stream);
+/* cos_sin[t][i] = mag * (cos, sin)(pos_of_tok[t] * freq[i]), i < half; the angle and its cos / sin in double. */
+int mrs_seq_rotation_table(const int32_t *pos_of_tok, const double *freq, int n_tok, int half, float mag, float *cos_sin,
+                           int64_t stream);
+/* attention: position i sees j <= i with i - j < window (window <= 0: all) or j < keep_first; sink f32 [heads] (NULL:
+ * none) adds exp(sink[h]) to the softmax denominator — a key without a value whose score is not scaled. */
+typedef struct {
+  const void *q;
+  int64_t q_ld;
+  const void *k_cache, *v_cache;
+  int dtype, heads, kv_heads, dk, dv;
+  float scale;
+  int window, keep_first;
+  const float *sink;
+  const int32_t *pages;
+  int pages_ld, page_size;
+  const int32_t *seq_of_tok, *pos_of_tok, *tok_index;
+  int n_tok;
+  void *out;
+  int64_t out_ld;
+  float out_scale;
+} mrs_seq_paged_attention_args;
+int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args, int64_t stream);
+/* Causal attention of sequences that START in this step over their own fresh q / k / v rows (bf16, dk = dv = d of 64 or
+ * 128, rows 16-byte aligned) on tensor cores, with the same window / keep_first / sink rule.  seq_rows [n_seq][2]: the
+ * first row and the row count of every such sequence inside q / k / v / out; longest = the largest row count. */
+int mrs_seq_prompt_attention(const void *q, const void *k, const void *v, void *out, const int32_t *seq_rows, int n_seq,
+                             int longest, int heads, int kv_heads, int d, int64_t q_ld, int64_t k_ld, int64_t v_ld, int64_t out_ld,
+                             float scale, int window, int keep_first, const float *sink, int64_t stream);
 /* x[r][c] *= scale for r < rows, c < cols (row stride ld) */
 int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream);
 
@@ -117,6 +202,12 @@ int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype, const int
                         int ff, int act, void *hidden, int64_t stream);
 int mrs_seq_moe_down(const void *hidden, const void *down, int dtype, const int32_t *experts, const float *weights, int n_tok,
                      int top, int width, int ff, void *out, int64_t stream);
+/* The plain rule: the `top` experts with the largest logits, weights = softmax over the chosen logits alone. */
+int mrs_seq_moe_route_top_softmax(const float *logits, int n_tok, int n_experts, int top, int32_t *experts, float *weights,
+                                  int64_t stream);
+/* Experts without a gate: hidden[t][k][:] = act(up[e] x_t), up [n_experts, ff, width]; followed by mrs_seq_moe_down. */
+int mrs_seq_moe_up(const void *x, const void *up, int dtype, const int32_t *experts, int n_tok, int top, int width, int ff,
+                   int act, void *hidden, int64_t stream);
 /* Large batches: rows sorted by expert.  counts[e] rows per expert, order[i] = the (token, k) pair (as token * top + k) at
  * sorted row i; gather copies x rows into sorted order, combine sums the experts' outputs back per token in k order. */
 int mrs_seq_moe_sort(const int32_t *experts, int n_pairs, int n_experts, int32_t *counts, int32_t *order, int64_t stream);

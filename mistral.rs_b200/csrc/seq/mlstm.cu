@@ -1,0 +1,131 @@
+// mlstm.cu — what surrounds the linear scan when it runs a stabilised matrix memory (the mLSTM of xLSTM):
+//
+//   m_t = max(f_t + m_(t-1), i_t)                     running maximum of the log gates, from 0
+//   S_t = exp(f_t + m_(t-1) - m_t) S_(t-1) + exp(i_t - m_t) k_t v_t^T        (n_t likewise, with k_t alone)
+//   y_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
+//
+// The recurrence itself is mrs_seq_linear_scan with per-token decay and input scale; the normaliser n rides along as
+// one more value column that is constantly 1.  Here: the gate kernel (soft cap, log-sigmoid, the running maximum as a
+// warp scan over 32 tokens at a time, carried per sequence), the ones column, and the output stage (denominator, unit
+// RMS per head, weight, sigmoid gate).  Everything is f32 except the value copy and the gate / output activations.
+#include "seq_common.cuh"
+
+namespace seq {
+
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float soft_cap_f(float z, float cap) { return cap > 0.0f ? cap * tanhf(z / cap) : z; }
+
+// one warp per (sequence, head).  Inside a block of 32 tokens with inclusive prefix sums F of f:
+//   m_l = F_l + max(m_start, max_{j <= l}(i_j - F_j))
+// which equals the token-by-token rule; keep / take are then formed from the m values actually stored, so they stay
+// consistent with them whatever the rounding of the scan.
+__global__ void mlstm_gates_kernel(const float *__restrict__ raw_in, const float *__restrict__ raw_forget, int64_t raw_ld, float cap, int heads,
+                                   float *__restrict__ m_state, const int32_t *__restrict__ cu_tok, const int32_t *__restrict__ past,
+                                   const int32_t *__restrict__ slot, int n_seq, float *__restrict__ keep, float *__restrict__ take,
+                                   float *__restrict__ m_tok) {
+  const int lane = threadIdx.x & 31;
+  const int job = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (job >= n_seq * heads) return;
+  const int b = job / heads, h = job % heads;
+  const int t_begin = cu_tok[b], t_end = cu_tok[b + 1];
+  if (t_end <= t_begin) return;
+  float *ms = m_state + (int64_t)slot[b] * heads + h;
+  float m_start = past[b] > 0 ? *ms : 0.0f;
+  for (int t0 = t_begin; t0 < t_end; t0 += 32) {
+    const int t = t0 + lane;
+    const bool live = t < t_end;
+    const float f = live ? log_sigmoid_f(soft_cap_f(raw_forget[(int64_t)t * raw_ld + h], cap)) : 0.0f;
+    const float i = live ? soft_cap_f(raw_in[(int64_t)t * raw_ld + h], cap) : -INFINITY;
+    float F = f;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float o = __shfl_up_sync(0xffffffffu, F, d);
+      if (lane >= d) F += o;
+    }
+    float G = i - F;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float o = __shfl_up_sync(0xffffffffu, G, d);
+      if (lane >= d) G = fmaxf(G, o);
+    }
+    const float m = F + fmaxf(m_start, G);
+    float before = __shfl_up_sync(0xffffffffu, m, 1);
+    if (lane == 0) before = m_start;
+    if (live) {
+      const int64_t at = (int64_t)t * heads + h;
+      keep[at] = expf(f + before - m);
+      take[at] = expf(i - m);
+      m_tok[at] = m;
+    }
+    m_start = __shfl_sync(0xffffffffu, m, 31);   // lanes past the end repeat the last live value (f = 0, i = -inf)
+  }
+  if (lane == 0) *ms = m_start;
+}
+
+template <typename T>
+__global__ void append_ones_kernel(const T *__restrict__ v, int64_t v_ld, int heads, int dv, int dvp, T *__restrict__ vaug) {
+  const int t = blockIdx.x, n = heads * dvp;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const int h = e / dvp, c = e % dvp;
+    vaug[(int64_t)t * n + e] = c < dv ? v[(int64_t)t * v_ld + h * dv + c] : from_f32<T>(c == dv ? 1.0f : 0.0f);
+  }
+}
+
+// one warp per (token, head)
+template <typename T>
+__global__ void mlstm_out_norm_kernel(const float *__restrict__ o, int dvp, const float *__restrict__ m_tok, float q_scale,
+                                      const T *__restrict__ gate, int64_t gate_ld, const float *__restrict__ weight, float eps, int heads,
+                                      int dv, T *__restrict__ out, int64_t out_ld, int n_tok) {
+  const int lane = threadIdx.x & 31;
+  const int64_t job = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (job >= (int64_t)n_tok * heads) return;
+  const int t = (int)(job / heads), h = (int)(job % heads);
+  const float *row = o + ((int64_t)t * heads + h) * dvp;
+  const float den = fmaxf(fabsf(q_scale * row[dv]), expf(-m_tok[(int64_t)t * heads + h])) + 1e-6f;
+  const float mul = q_scale / den;
+  float ss = 0.0f;
+  for (int c = lane; c < dv; c += 32) {
+    const float y = row[c] * mul;
+    ss = fmaf(y, y, ss);
+  }
+  const float inv = rsqrtf_exact(warp_sum(ss) / (float)dv + eps);
+  const T *g = gate + (int64_t)t * gate_ld + h * dv;
+  const float *w = weight + h * dv;
+  T *dst = out + (int64_t)t * out_ld + h * dv;
+  for (int c = lane; c < dv; c += 32) dst[c] = from_f32<T>(row[c] * mul * inv * w[c] * sigmoid_f(to_f32<T>(g[c])));
+}
+
+}  // namespace seq
+
+using namespace seq;
+
+extern "C" int mrs_seq_mlstm_gates(const float *raw_in, const float *raw_forget, int64_t raw_ld, float cap, int heads, float *m_state,
+                                   const int32_t *cu_tok, const int32_t *past, const int32_t *slot, int n_seq, int n_tok, float *keep,
+                                   float *take, float *m_tok, int64_t stream) {
+  if (n_tok <= 0 || n_seq <= 0) return 0;
+  if (heads <= 0 || !raw_in || !raw_forget || !m_state || !keep || !take || !m_tok) return -2;
+  const int warps = 4, jobs = n_seq * heads;
+  mlstm_gates_kernel<<<(jobs + warps - 1) / warps, warps * 32, 0, (cudaStream_t)stream>>>(raw_in, raw_forget, raw_ld, cap, heads, m_state,
+                                                                                       cu_tok, past, slot, n_seq, keep, take, m_tok);
+  return launch_status();
+}
+
+extern "C" int mrs_seq_append_ones(const void *v, int64_t v_ld, int dtype, int heads, int dv, int dvp, int n_tok, void *vaug,
+                                   int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (heads <= 0 || dv <= 0 || dvp <= dv) return -2;
+  SEQ_DISPATCH_DTYPE(dtype, (append_ones_kernel<T><<<n_tok, 256, 0, (cudaStream_t)stream>>>((const T *)v, v_ld, heads, dv, dvp, (T *)vaug)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_mlstm_out_norm(const float *o, int dvp, const float *m_tok, float q_scale, const void *gate, int64_t gate_ld,
+                                      const float *weight, float eps, int heads, int dv, void *out, int64_t out_ld, int dtype, int n_tok,
+                                      int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (heads <= 0 || dv <= 0 || dvp <= dv) return -2;
+  const int warps = 4;
+  const int64_t jobs = (int64_t)n_tok * heads;
+  SEQ_DISPATCH_DTYPE(dtype, (mlstm_out_norm_kernel<T><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, 0, (cudaStream_t)stream>>>(
+                                o, dvp, m_tok, q_scale, (const T *)gate, gate_ld, weight, eps, heads, dv, (T *)out, out_ld, n_tok)));
+  return launch_status();
+}

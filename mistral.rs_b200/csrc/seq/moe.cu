@@ -114,6 +114,62 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T *__restrict__ 
   }
 }
 
+// the plain rule, one warp per token: the `top` largest logits (ties: the lower index), softmax over those alone
+__global__ void moe_route_top_softmax_kernel(const float *__restrict__ logits, int n_tok, int n_experts, int top,
+                                             int32_t *__restrict__ experts, float *__restrict__ weights) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int t = blockIdx.x * nw + wib;
+  if (t >= n_tok) return;
+  float *z = sm + (size_t)wib * n_experts;
+  for (int e = lane; e < n_experts; e += 32) z[e] = logits[(int64_t)t * n_experts + e];
+  __syncwarp();
+  float first = 0.0f, sum = 0.0f;
+  for (int r = 0; r < top; r++) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float v = z[e];
+      if (v == v && (bi == 0x7fffffff ? v >= bv : v > bv)) { bv = v; bi = e; }   // NaN never wins; a taken expert holds NaN
+    }
+    for (int m = 16; m > 0; m >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    if (bi == 0x7fffffff) { bi = 0; bv = -INFINITY; }
+    if (r == 0) first = bv;                       // the largest logit: the softmax's reference point
+    const float p = expf(bv - first);
+    sum += p;
+    if (lane == 0) {
+      experts[(int64_t)t * top + r] = bi;
+      weights[(int64_t)t * top + r] = p;
+      z[bi] = __int_as_float(0x7fc00000);
+    }
+    __syncwarp();
+  }
+  if (lane == 0)
+    for (int r = 0; r < top; r++) weights[(int64_t)t * top + r] /= sum;
+}
+
+// hidden[t][k][r] = act(up[e][r] . x_t): experts without a gate; the layout of moe_gate_up_kernel
+template <typename T>
+__global__ void __launch_bounds__(256) moe_up_kernel(const T *__restrict__ x, const T *__restrict__ up, const int32_t *__restrict__ experts,
+                                                     int top, int width, int ff, int act, T *__restrict__ hidden) {
+  extern __shared__ __align__(16) float xs[];   // [width]
+  const int pair = blockIdx.y, tok = pair / top;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int e = experts[pair];
+  for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32<T>(x[(int64_t)tok * width + c]);
+  __syncthreads();
+  const T *w = up + (int64_t)e * ff * width;
+  const bool vec = width % Vec16<T>::N == 0 && ((uintptr_t)up % 16) == 0;
+  for (int r = blockIdx.x * nw + wib; r < ff; r += gridDim.x * nw) {
+    const float a = warp_row_dot<T>(w + (int64_t)r * width, xs, width, lane, vec);
+    if (lane == 0) hidden[(int64_t)pair * ff + r] = from_f32<T>(apply_act(to_f32<T>(from_f32<T>(a)), act));
+  }
+}
+
 // out[t][r] = sum_k weights[t][k] * (down[e_k][r] . hidden[t][k])
 template <typename T>
 __global__ void __launch_bounds__(256) moe_down_kernel(const T *__restrict__ hidden, const T *__restrict__ down,
@@ -195,6 +251,35 @@ extern "C" int mrs_seq_moe_route(const float *logits, const float *correction, i
   const size_t bytes = (size_t)warps * (2 * n_experts + n_groups) * sizeof(float);
   moe_route_kernel<<<(n_tok + warps - 1) / warps, warps * 32, bytes, (cudaStream_t)stream>>>(
       logits, correction, n_tok, n_experts, n_groups, keep_groups, top, renorm, experts, weights);
+  return launch_status();
+}
+
+extern "C" int mrs_seq_moe_route_top_softmax(const float *logits, int n_tok, int n_experts, int top, int32_t *experts, float *weights,
+                                             int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (n_experts < 1 || n_experts > ROUTE_MAX_EXPERTS || top < 1 || top > n_experts) return -2;
+  const int warps = 4;
+  moe_route_top_softmax_kernel<<<(n_tok + warps - 1) / warps, warps * 32, (size_t)warps * n_experts * sizeof(float), (cudaStream_t)stream>>>(
+      logits, n_tok, n_experts, top, experts, weights);
+  return launch_status();
+}
+
+extern "C" int mrs_seq_moe_up(const void *x, const void *up, int dtype, const int32_t *experts, int n_tok, int top, int width, int ff,
+                              int act, void *hidden, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if ((size_t)width * sizeof(float) > 160 * 1024) return -2;
+  const int warps = 8, bx = (ff + warps - 1) / warps;
+  const size_t bytes = (size_t)width * sizeof(float);
+  SEQ_DISPATCH_DTYPE(dtype, {
+    auto kern = moe_up_kernel<T>;
+    static size_t allowed = 48 * 1024;
+    if (bytes > allowed) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+      allowed = bytes;
+    }
+    kern<<<dim3(bx < 256 ? bx : 256, n_tok * top), warps * 32, bytes, (cudaStream_t)stream>>>((const T *)x, (const T *)up, experts, top, width,
+                                                                                             ff, act, (T *)hidden);
+  });
   return launch_status();
 }
 

@@ -25,6 +25,8 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
+__device__ __forceinline__ float relu_sq_f(float z) { return z > 0.0f ? z * z : 0.0f; }
 __device__ __forceinline__ float rsqrtf_exact(float x) { return 1.0f / sqrtf(x); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ float apply_act(float z, int act) {
@@ -32,6 +34,8 @@ __device__ __forceinline__ float apply_act(float z, int act) {
     case MRS_SEQ_ACT_SILU: return silu_f(z);
     case MRS_SEQ_ACT_GELU_TANH: return gelu_tanh_f(z);
     case MRS_SEQ_ACT_SIGMOID: return sigmoid_f(z);
+    case MRS_SEQ_ACT_GELU_ERF: return gelu_erf_f(z);
+    case MRS_SEQ_ACT_RELU_SQ: return relu_sq_f(z);
     default: return z;
   }
 }

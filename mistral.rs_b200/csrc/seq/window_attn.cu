@@ -1,44 +1,101 @@
-// window_attn.cu — softmax attention over a paged cache for layers whose scores carry no position signal: per-head
-// RMS norm of queries and keys, a sliding window (or full causal reach), grouped key/value heads, and key / value
-// head sizes that need not match.  The new tokens' keys and values are stored first; the attention kernel then reads
+// window_attn.cu — softmax attention over a paged cache: RMS norm of queries and keys (per head, or over the whole
+// projection), optional rotary positions on part of every head, a sliding window (or full causal reach) that may keep
+// the first tokens of the sequence in sight, an optional per-head sink in the softmax denominator, grouped key/value
+// heads, values that may be the unnormed keys, and key / value head sizes that need not match.  The new tokens' keys and values are stored first; the attention kernel then reads
 // every key of a query, old or new, from the pages — one code path for a prompt portion and for a decoded token.
 #include "seq_common.cuh"
 
 namespace seq {
 
-// one warp per (token, head) for q; warps past the q heads take the k heads (norm + store) and the v heads (store)
+// Query / key preparation, one CTA per token.  Phase 1: sums of squares per head (one warp per q or k head).  Phase 2,
+// again one warp per head: the RMS norm (per head with weights shared by the heads, or over the whole projection at
+// once with one weight per element), the rotation of the first rot_dims entries in pairs (i, i + rot_dims / 2) by the
+// step's cos / sin table, q and k rewritten in place, k stored to its cache slot; values stored from their own
+// projection or — v == NULL — from the keys as they were projected (read before the key is rewritten).
 template <typename T>
-__global__ void qk_norm_store_kernel(T *__restrict__ q, int64_t q_ld, T *__restrict__ k, int64_t k_ld, const T *__restrict__ v,
-                                     int64_t v_ld, const float *__restrict__ q_norm_w, const float *__restrict__ k_norm_w,
-                                     float eps, int heads, int kv_heads, int dk, int dv, T *__restrict__ k_cache,
-                                     T *__restrict__ v_cache, const int64_t *__restrict__ slot_of_tok) {
-  const int t = blockIdx.x, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int64_t slot = slot_of_tok[t];
-  for (int job = threadIdx.x >> 5; job < heads + 2 * kv_heads; job += nw) {
+__global__ void attention_prepare_kernel(const mrs_seq_attn_prepare_args a) {
+  extern __shared__ float ss[];   // [heads + kv_heads] sums of squares
+  const int t = blockIdx.x, lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int heads = a.heads, kv_heads = a.kv_heads, dk = a.dk, dv = a.dv;
+  T *q = (T *)a.q + (int64_t)t * a.q_ld, *k = (T *)a.k + (int64_t)t * a.k_ld;
+  const int64_t slot = a.slot_of_tok[t];
+  if (a.norm_mode != MRS_SEQ_QK_NORM_NONE) {
+    for (int job = wib; job < heads + kv_heads; job += nw) {
+      const T *src = job < heads ? q + job * dk : k + (job - heads) * dk;
+      float s = 0.0f;
+      for (int d = lane; d < dk; d += 32) {
+        const float x = to_f32<T>(src[d]);
+        s = fmaf(x, x, s);
+      }
+      s = warp_sum(s);
+      if (lane == 0) ss[job] = s;
+    }
+    __syncthreads();
+  }
+  float inv_q_all = 1.0f, inv_k_all = 1.0f;
+  if (a.norm_mode == MRS_SEQ_QK_NORM_WHOLE) {
+    float sq = 0.0f, sk = 0.0f;
+    for (int h = 0; h < heads; h++) sq += ss[h];
+    for (int h = 0; h < kv_heads; h++) sk += ss[heads + h];
+    inv_q_all = rsqrtf_exact(sq / (float)(heads * dk) + a.eps);
+    inv_k_all = rsqrtf_exact(sk / (float)(kv_heads * dk) + a.eps);
+  }
+  const int half = a.cos_sin ? a.rot_dims / 2 : 0;
+  const float2 *cs = (const float2 *)a.cos_sin + (int64_t)t * half;
+  for (int job = wib; job < heads + 2 * kv_heads; job += nw) {
     if (job < heads + kv_heads) {
       const bool is_q = job < heads;
       const int hh = is_q ? job : job - heads;
-      T *src = is_q ? q + (int64_t)t * q_ld + hh * dk : k + (int64_t)t * k_ld + hh * dk;
-      const float *w = is_q ? q_norm_w : k_norm_w;
-      float ss = 0.0f;
-      for (int d = lane; d < dk; d += 32) {
-        const float x = to_f32<T>(src[d]);
-        ss = fmaf(x, x, ss);
+      T *src = is_q ? q + hh * dk : k + hh * dk;
+      const float *w = is_q ? a.q_norm_w : a.k_norm_w;
+      float inv = 1.0f;
+      if (a.norm_mode == MRS_SEQ_QK_NORM_HEAD) inv = rsqrtf_exact(ss[job] / (float)dk + a.eps);
+      else if (a.norm_mode == MRS_SEQ_QK_NORM_WHOLE) { inv = is_q ? inv_q_all : inv_k_all; w += hh * dk; }
+      const bool normed = a.norm_mode != MRS_SEQ_QK_NORM_NONE;
+      T *cached = (!is_q && slot >= 0) ? (T *)a.k_cache + (slot * kv_heads + hh) * dk : nullptr;
+      if (!is_q && a.v == nullptr) {      // the values are the keys as projected
+        T *vc = slot >= 0 ? (T *)a.v_cache + (slot * kv_heads + hh) * dv : nullptr;
+        T *cp = a.v_copy ? (T *)a.v_copy + (int64_t)t * a.v_copy_ld + hh * dk : nullptr;
+        for (int d = lane; d < dk; d += 32) {
+          const T raw = src[d];
+          if (vc) vc[d] = raw;
+          if (cp) cp[d] = raw;
+        }
+        __syncwarp();
       }
-      const float inv = w ? rsqrtf_exact(warp_sum(ss) / (float)dk + eps) : 1.0f;
-      T *cached = (!is_q && slot >= 0) ? k_cache + (slot * kv_heads + hh) * dk : nullptr;
-      for (int d = lane; d < dk; d += 32) {   // normed in place (a prompt kernel may read q and k from here), k also to its page
-        const T r = from_f32<T>(w ? to_f32<T>(src[d]) * inv * w[d] : to_f32<T>(src[d]));
+      for (int i = lane; i < half; i += 32) {          // rotated pairs
+        const float u = normed ? to_f32<T>(src[i]) * inv * w[i] : to_f32<T>(src[i]);
+        const float v = normed ? to_f32<T>(src[i + half]) * inv * w[i + half] : to_f32<T>(src[i + half]);
+        const float2 c = cs[i];
+        const T ru = from_f32<T>(u * c.x - v * c.y), rv = from_f32<T>(v * c.x + u * c.y);
+        src[i] = ru;
+        src[i + half] = rv;
+        if (cached) { cached[i] = ru; cached[i + half] = rv; }
+      }
+      for (int d = 2 * half + lane; d < dk; d += 32) {  // the rest passes
+        const T r = normed ? from_f32<T>(to_f32<T>(src[d]) * inv * w[d]) : src[d];
         src[d] = r;
         if (cached) cached[d] = r;
       }
-    } else if (slot >= 0) {
+    } else if (slot >= 0 && a.v != nullptr) {
       const int hh = job - heads - kv_heads;
-      const T *src = v + (int64_t)t * v_ld + hh * dv;
-      T *dst = v_cache + (slot * kv_heads + hh) * dv;
+      const T *src = (const T *)a.v + (int64_t)t * a.v_ld + hh * dv;
+      T *dst = (T *)a.v_cache + (slot * kv_heads + hh) * dv;
       for (int d = lane; d < dv; d += 32) dst[d] = src[d];
     }
   }
+}
+
+// cos_sin[t][i] = mag * (cos, sin)(pos[t] * freq[i]): the angle, and its reduction, in double — positions in the thousands
+// times a frequency near one leave no digits to spare in f32
+__global__ void rotation_table_kernel(const int32_t *__restrict__ pos_of_tok, const double *__restrict__ freq, int n_tok, int half,
+                                      float mag, float2 *__restrict__ cos_sin) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_tok * half) return;
+  const int t = e / half, i = e % half;
+  double s, c;
+  sincos((double)pos_of_tok[t] * freq[i], &s, &c);
+  cos_sin[e] = make_float2((float)(c * (double)mag), (float)(s * (double)mag));
 }
 
 // One warp per (token, head).  32 keys per round: lane j scores key j against the whole query (held in shared
@@ -47,7 +104,8 @@ __global__ void qk_norm_store_kernel(T *__restrict__ q, int64_t q_ld, T *__restr
 template <typename T, int MAX_VCOLS>   // MAX_VCOLS * 32 >= value head size
 __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restrict__ q, int64_t q_ld, const T *__restrict__ k_cache,
                                                                const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
-                                                               float scale, int window, const int32_t *__restrict__ pages,
+                                                               float scale, int window, int keep_first, const float *__restrict__ sink,
+                                                               const int32_t *__restrict__ pages,
                                                                int pages_ld, int page_size, const int32_t *__restrict__ seq_of_tok,
                                                                const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index,
                                                                int n_tok, T *__restrict__ out, int64_t out_ld, float out_scale) {
@@ -65,11 +123,14 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
   float m = -INFINITY, l = 0.0f, acc[MAX_VCOLS];
 #pragma unroll
   for (int c = 0; c < MAX_VCOLS; c++) acc[c] = 0.0f;
-  for (int j0 = lo; j0 <= pos; j0 += 32) {
+  const int kept = min(keep_first, lo);                       // kept first keys that lie before the window: [0, kept)
+  const int kept_rounds = (kept + 31) / 32, rounds = kept_rounds + (pos - lo) / 32 + 1;
+  for (int r = 0; r < rounds; r++) {
+    const int j0 = r < kept_rounds ? r * 32 : lo + (r - kept_rounds) * 32, jend = r < kept_rounds ? kept : pos + 1;
     const int j = j0 + lane;
     float sc = -INFINITY;
     int64_t slot = 0;
-    if (j <= pos) {
+    if (j < jend) {
       slot = (int64_t)table[j / page_size] * page_size + j % page_size;
       const T *kr = k_cache + (slot * kv_heads + g) * dk;
       float a0 = 0.0f, a1 = 0.0f;
@@ -81,13 +142,13 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
       if (d < dk) a0 = fmaf(qv[d], to_f32<T>(kr[d]), a0);
       sc = a0 + a1;
     }
-    const float m_new = fmaxf(m, warp_max(sc));      // the round always holds key j0 <= pos: m_new is finite
-    const float p = j <= pos ? expf(sc - m_new) : 0.0f;
+    const float m_new = fmaxf(m, warp_max(sc));      // the round always holds key j0 < jend: m_new is finite
+    const float p = j < jend ? expf(sc - m_new) : 0.0f;
     const float corr = expf(m - m_new);               // exp(-inf) = 0 on the first round
     l = l * corr + warp_sum(p);
 #pragma unroll
     for (int c = 0; c < MAX_VCOLS; c++) acc[c] *= corr;
-    const int n = min(32, pos - j0 + 1);
+    const int n = min(32, jend - j0);
     for (int i = 0; i < n; i++) {
       const float pi = __shfl_sync(0xffffffffu, p, i);
       const int64_t si = __shfl_sync(0xffffffffu, slot, i);
@@ -98,6 +159,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
     }
     m = m_new;
   }
+  if (sink) l += expf(sink[h] - m);                  // a key without a value; its score is not scaled
   const float inv = out_scale / l;
 #pragma unroll
   for (int c = 0; c < MAX_VCOLS; c++)
@@ -111,8 +173,9 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
 template <typename T, int VPAIRS, int SPLIT>   // VPAIRS * 64 >= dv
 __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
     const T *__restrict__ q, int64_t q_ld, const T *__restrict__ k_cache, const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
-    float scale, int window, const int32_t *__restrict__ pages, int pages_ld, int page_size, const int32_t *__restrict__ seq_of_tok,
-    const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index, T *__restrict__ out, int64_t out_ld, float out_scale) {
+    float scale, int window, int keep_first, const float *__restrict__ sink, const int32_t *__restrict__ pages, int pages_ld, int page_size,
+    const int32_t *__restrict__ seq_of_tok, const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index, T *__restrict__ out,
+    int64_t out_ld, float out_scale) {
   extern __shared__ __align__(16) float sm[];   // q [dk] | per warp: m, l, acc [VPAIRS * 64]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int ti = blockIdx.x / heads, h = blockIdx.x % heads, t = tok_index ? tok_index[ti] : ti, g = h / (heads / kv_heads);
@@ -127,11 +190,14 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
 #pragma unroll
   for (int c = 0; c < VPAIRS; c++) acc[c] = make_float2(0.0f, 0.0f);
   constexpr int N = Vec16<T>::N;
-  for (int j0 = lo + wib * 32; j0 <= pos; j0 += SPLIT * 32) {
+  const int kept = min(keep_first, lo);                       // kept first keys that lie before the window: [0, kept)
+  const int kept_rounds = (kept + 31) / 32, rounds = kept_rounds + (pos - lo) / 32 + 1;
+  for (int r = wib; r < rounds; r += SPLIT) {
+    const int j0 = r < kept_rounds ? r * 32 : lo + (r - kept_rounds) * 32, jend = r < kept_rounds ? kept : pos + 1;
     const int j = j0 + lane;
     float sc = -INFINITY;
     int64_t slot = 0;
-    if (j <= pos) {
+    if (j < jend) {
       slot = (int64_t)table[j / page_size] * page_size + j % page_size;
       const T *kr = k_cache + (slot * kv_heads + g) * dk;
       float a0 = 0.0f, a1 = 0.0f;
@@ -145,12 +211,12 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
       sc = a0 + a1;
     }
     const float m_new = fmaxf(m, warp_max(sc));
-    const float p = j <= pos ? expf(sc - m_new) : 0.0f;
+    const float p = j < jend ? expf(sc - m_new) : 0.0f;
     const float corr = expf(m - m_new);
     l = l * corr + warp_sum(p);
 #pragma unroll
     for (int c = 0; c < VPAIRS; c++) { acc[c].x *= corr; acc[c].y *= corr; }
-    const int n = min(32, pos - j0 + 1);
+    const int n = min(32, jend - j0);
     // eight keys per pass: their value rows are fetched together, so the loads overlap instead of queueing behind the
     // shuffles that carry each key's slot
     for (int i0 = 0; i0 < n; i0 += 8) {
@@ -189,6 +255,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
     const float mw = part[w * (2 + VPAIRS * 64)];
     if (mw != -INFINITY) lsum += part[w * (2 + VPAIRS * 64) + 1] * expf(mw - mx);
   }
+  if (sink) lsum += expf(sink[h] - mx);              // warp 0 always holds a key: mx is finite
   const float inv = out_scale / lsum;
   for (int c = threadIdx.x; c < dv; c += SPLIT * 32) {
     float o = 0.0f;
@@ -210,32 +277,55 @@ __global__ void scale_rows_kernel(T *__restrict__ x, int64_t ld, int cols, float
 
 using namespace seq;
 
-extern "C" int mrs_seq_qk_norm_store(void *q, int64_t q_ld, void *k, int64_t k_ld, const void *v, int64_t v_ld, int dtype,
-                                     const float *q_norm_w, const float *k_norm_w, float eps, int heads, int kv_heads, int dk, int dv,
-                                     void *k_cache, void *v_cache, const int64_t *slot_of_tok, int n_tok, int64_t stream) {
-  if (n_tok <= 0) return 0;
-  const int jobs = heads + 2 * kv_heads, warps = jobs < 8 ? jobs : 8;
-  SEQ_DISPATCH_DTYPE(dtype, (qk_norm_store_kernel<T><<<n_tok, warps * 32, 0, (cudaStream_t)stream>>>(
-                                (T *)q, q_ld, (T *)k, k_ld, (const T *)v, v_ld, q_norm_w, k_norm_w, eps, heads, kv_heads, dk, dv,
-                                (T *)k_cache, (T *)v_cache, slot_of_tok)));
+extern "C" int mrs_seq_attention_prepare(const mrs_seq_attn_prepare_args *args, int64_t stream) {
+  const mrs_seq_attn_prepare_args &a = *args;
+  if (a.n_tok <= 0) return 0;
+  if (a.heads <= 0 || a.kv_heads <= 0 || a.dk <= 0 || a.dv <= 0 || !a.q || !a.k || !a.slot_of_tok) return -2;
+  if (a.norm_mode != MRS_SEQ_QK_NORM_NONE && (!a.q_norm_w || !a.k_norm_w)) return -2;
+  if (a.v == nullptr && a.dv != a.dk) return -2;
+  if (a.cos_sin && (a.rot_dims < 2 || a.rot_dims % 2 || a.rot_dims > a.dk)) return -2;
+  const int jobs = a.heads + 2 * a.kv_heads, warps = jobs < 8 ? jobs : 8;
+  const size_t bytes = (size_t)(a.heads + a.kv_heads) * sizeof(float);
+  SEQ_DISPATCH_DTYPE(a.dtype, (attention_prepare_kernel<T><<<a.n_tok, warps * 32, bytes, (cudaStream_t)stream>>>(a)));
   return launch_status();
 }
 
-extern "C" int mrs_seq_window_attention(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, int dtype, int heads,
-                                        int kv_heads, int dk, int dv, float scale, int window, const int32_t *pages, int pages_ld,
-                                        int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, const int32_t *tok_index,
-                                        int n_tok, void *out, int64_t out_ld, float out_scale, int64_t stream) {
+extern "C" int mrs_seq_qk_norm_store(void *q, int64_t q_ld, void *k, int64_t k_ld, const void *v, int64_t v_ld, int dtype,
+                                     const float *q_norm_w, const float *k_norm_w, float eps, int heads, int kv_heads, int dk, int dv,
+                                     void *k_cache, void *v_cache, const int64_t *slot_of_tok, int n_tok, int64_t stream) {
+  if (!v) return -2;
+  mrs_seq_attn_prepare_args a = {};
+  a.q = q; a.k = k; a.v = v; a.q_ld = q_ld; a.k_ld = k_ld; a.v_ld = v_ld;
+  a.dtype = dtype; a.norm_mode = (q_norm_w && k_norm_w) ? MRS_SEQ_QK_NORM_HEAD : MRS_SEQ_QK_NORM_NONE;
+  a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.eps = eps;
+  a.heads = heads; a.kv_heads = kv_heads; a.dk = dk; a.dv = dv;
+  a.k_cache = k_cache; a.v_cache = v_cache; a.slot_of_tok = slot_of_tok; a.n_tok = n_tok;
+  return mrs_seq_attention_prepare(&a, stream);
+}
+
+extern "C" int mrs_seq_rotation_table(const int32_t *pos_of_tok, const double *freq, int n_tok, int half, float mag, float *cos_sin,
+                                      int64_t stream) {
+  if (n_tok <= 0 || half <= 0) return 0;
+  const int total = n_tok * half;
+  rotation_table_kernel<<<(total + 127) / 128, 128, 0, (cudaStream_t)stream>>>(pos_of_tok, freq, n_tok, half, mag, (float2 *)cos_sin);
+  return launch_status();
+}
+
+extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args, int64_t stream) {
+  const mrs_seq_paged_attention_args &a = *args;
+  const int n_tok = a.n_tok, heads = a.heads, kv_heads = a.kv_heads, dk = a.dk, dv = a.dv, dtype = a.dtype;
   if (n_tok <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 512 || dk > 1024) return -2;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 512 || dk > 1024 || a.page_size <= 0) return -2;
+  const int keep_first = a.keep_first > 0 ? a.keep_first : 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int elem = dtype == MRS_SEQ_BF16 ? 2 : 4;
-  const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 256 && ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 8) == 0;
+  const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 256 && ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 8) == 0;
   if (vec) {
     constexpr int SPLIT = 8;
 #define SEQ_ATTN_VEC(VP)                                                                                                         \
   window_attention_vec_kernel<T, VP, SPLIT><<<(unsigned)n_tok * heads, SPLIT * 32, (dk + SPLIT * (2 + VP * 64)) * sizeof(float), st>>>( \
-      (const T *)q, q_ld, (const T *)k_cache, (const T *)v_cache, heads, kv_heads, dk, dv, scale, window, pages, pages_ld, page_size,   \
-      seq_of_tok, pos_of_tok, tok_index, (T *)out, out_ld, out_scale)
+      (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink,  \
+      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, (T *)a.out, a.out_ld, a.out_scale)
     SEQ_DISPATCH_DTYPE(dtype, {
       if (dv <= 64) SEQ_ATTN_VEC(1);
       else if (dv <= 128) SEQ_ATTN_VEC(2);
@@ -248,8 +338,8 @@ extern "C" int mrs_seq_window_attention(const void *q, int64_t q_ld, const void 
   const int64_t jobs = (int64_t)n_tok * heads;
 #define SEQ_ATTN_LAUNCH(VC)                                                                                              \
   window_attention_kernel<T, VC><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, warps * dk * sizeof(float), st>>>(  \
-      (const T *)q, q_ld, (const T *)k_cache, (const T *)v_cache, heads, kv_heads, dk, dv, scale, window, pages, pages_ld, \
-      page_size, seq_of_tok, pos_of_tok, tok_index, n_tok, (T *)out, out_ld, out_scale)
+      (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink, \
+      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, n_tok, (T *)a.out, a.out_ld, a.out_scale)
   SEQ_DISPATCH_DTYPE(dtype, {
     if (dv <= 64) SEQ_ATTN_LAUNCH(2);
     else if (dv <= 128) SEQ_ATTN_LAUNCH(4);
@@ -258,6 +348,20 @@ extern "C" int mrs_seq_window_attention(const void *q, int64_t q_ld, const void 
   });
 #undef SEQ_ATTN_LAUNCH
   return launch_status();
+}
+
+extern "C" int mrs_seq_window_attention(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, int dtype, int heads,
+                                        int kv_heads, int dk, int dv, float scale, int window, const int32_t *pages, int pages_ld,
+                                        int page_size, const int32_t *seq_of_tok, const int32_t *pos_of_tok, const int32_t *tok_index,
+                                        int n_tok, void *out, int64_t out_ld, float out_scale, int64_t stream) {
+  mrs_seq_paged_attention_args a = {};
+  a.q = q; a.q_ld = q_ld; a.k_cache = k_cache; a.v_cache = v_cache;
+  a.dtype = dtype; a.heads = heads; a.kv_heads = kv_heads; a.dk = dk; a.dv = dv;
+  a.scale = scale; a.window = window;
+  a.pages = pages; a.pages_ld = pages_ld; a.page_size = page_size;
+  a.seq_of_tok = seq_of_tok; a.pos_of_tok = pos_of_tok; a.tok_index = tok_index; a.n_tok = n_tok;
+  a.out = out; a.out_ld = out_ld; a.out_scale = out_scale;
+  return mrs_seq_paged_attention(&a, stream);
 }
 
 extern "C" int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream) {

@@ -101,8 +101,9 @@ class StepBatch:
         is_fresh = [p == 0 and c >= self.FRESH_MIN for p, c in zip(pasts, counts)]
         self.fresh = [(int(cu[b]), int(counts[b])) for b in range(n_seq) if is_fresh[b]]      # (first row, rows) per such sequence
         paged = np.concatenate([np.arange(cu[b], cu[b + 1], dtype=np.int32) for b in range(n_seq) if not is_fresh[b]] + [np.zeros(0, np.int32)])
+        fresh_rows = np.asarray(self.fresh, dtype=np.int32).reshape(-1)                        # (first row, rows) pairs for the kernels
         parts = [np.asarray(ids, dtype=np.int32), cu, np.asarray(pasts, dtype=np.int32), np.asarray(slots, dtype=np.int32), seq_of, pos_of,
-                 pages.reshape(-1), np.asarray(rows, dtype=np.int32), paged]
+                 pages.reshape(-1), np.asarray(rows, dtype=np.int32), paged, fresh_rows]
         sizes = [p.size for p in parts]
         pad = sum(sizes) % 2                                       # keep the int64 tail 8-byte aligned
         total = sum(sizes) + pad + 2 * n_tok
@@ -127,6 +128,7 @@ class StepBatch:
         self.pages = cut(6).view(n_seq, pages_ld)
         self.rows = cut(7)
         self.paged_tok = cut(8)                                    # tokens of the sequences not in `fresh`
+        self.fresh_rows = cut(9)
         at = int(o[-1]) + pad
         self.slot_of_tok = dev[at:at + 2 * n_tok].view(torch.int64)
 

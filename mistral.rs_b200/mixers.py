@@ -1,6 +1,8 @@
 """Layer mechanisms built on the sequence-mixer kernels (`seq_ops`), each with its constants as parameters so any
-model definition can compose them: multi-stream residuals, linear attention with per-head decay, windowed attention
-with query/key norm over a paged cache, a Mamba-2 style state-space mixer, two mixers side by side, dense GLU and
+model definition can compose them: multi-stream residuals, Dynamic Tanh norms around a single residual, linear
+attention with per-head decay, a stabilised matrix memory (mLSTM), softmax attention over a paged cache (query/key
+norm per head or over the whole projection, rotary positions with scaled frequencies, window with kept first tokens,
+sink, values that are the keys), a Mamba-2 style state-space mixer, two mixers side by side, dense GLU / plain and
 routed-expert feed-forwards.
 
 A mechanism owns its device weights and declares the per-layer cache it needs (`alloc_cache`): token-indexed pages
@@ -47,43 +49,147 @@ class LinearAttentionMixer:
         return linear(on, self.w_o)
 
 
-class WindowAttention:
-    """Grouped-query softmax attention without positional rotation: per-head RMS norm of q and k, scores scaled by a
-    given constant, a sliding window of `window` positions (0: full causal), keys and values in pages."""
+class TanhNorm:
+    """Dynamic Tanh: tanh(alpha z) * weight + bias — a norm that computes no statistics.  `t` is what the kernels take."""
 
-    def __init__(self, heads, kv_heads, dk, dv, scale, window, q_norm_w, k_norm_w, eps):
+    def __init__(self, alpha, weight, bias):
+        self.t = (alpha, weight, bias)
+
+
+class Rotation:
+    """Rotary positions on the first `dims` entries of every head, pairs (i, i + dims / 2), frequency base^(-2i/dims).
+    `scaling` (YaRN: factor, original, fast, slow) divides the slow frequencies by `factor` along a linear ramp between
+    the pair indices at which `original` positions make `fast` and `slow` turns, and multiplies cos and sin by
+    0.1 ln(factor) + 1.  Frequencies are formed in double on the host; the table of a step (one per distinct
+    rotation, shared by the layers that use it) comes from `seq_ops.rotation_table`."""
+
+    def __init__(self, dims, base, scaling, device):
+        import math
+        dims, base = int(dims), float(base)
+        if dims < 2 or dims % 2:
+            raise ValueError("rotated dimensions come in pairs")
+        freq, self.mag = [base ** (-2.0 * i / dims) for i in range(dims // 2)], 1.0
+        if scaling:
+            factor, orig = float(scaling["factor"]), float(scaling["original"])
+            turn = lambda t: dims * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+            lo, hi = max(math.floor(turn(float(scaling["fast"]))), 0), min(math.ceil(turn(float(scaling["slow"]))), dims - 1)
+            ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(dims // 2)]
+            freq = [f / factor * r + f * (1.0 - r) for f, r in zip(freq, ramp)]
+            self.mag = 0.1 * math.log(factor) + 1.0
+        self.dims = dims
+        self.key = (dims, base, tuple(sorted((k, float(v)) for k, v in scaling.items())) if scaling else None)
+        self.freq = torch.tensor(freq, dtype=torch.float64, device=device)
+
+    def table(self, batch):
+        tables = batch.__dict__.setdefault("_rotation_tables", {})
+        if self.key not in tables:
+            tables[self.key] = K.rotation_table(batch.pos_of_tok, self.freq, self.mag)
+        return tables[self.key]
+
+
+class WindowAttention:
+    """Grouped-query softmax attention over pages.  Queries and keys: RMS norm per head with weights shared by the
+    heads (`norm_mode` QK_NORM_HEAD), over the whole projection at once (QK_NORM_WHOLE) or none; then `rotation` (None:
+    scores carry no position).  Scores are scaled by a given constant.  Position i sees j <= i with i - j < `window`
+    (0: full causal) or j < `keep_first`; `sink` [heads] adds exp(sink) to the softmax denominator.  With
+    `values_from_keys` there is no value projection: the values are the keys as projected, before norm and rotation."""
+
+    def __init__(self, heads, kv_heads, dk, dv, scale, window, q_norm_w, k_norm_w, eps, norm_mode=K.QK_NORM_HEAD, rotation=None,
+                 keep_first=0, sink=None, values_from_keys=False):
+        if values_from_keys and dk != dv:
+            raise ValueError("values that are the keys need equal key and value head sizes")
+        if heads % kv_heads:
+            raise ValueError("query heads must be a multiple of key/value heads")
         self.heads, self.kv_heads, self.dk, self.dv = heads, kv_heads, dk, dv
         self.scale, self.window, self.q_norm_w, self.k_norm_w, self.eps = scale, window, q_norm_w, k_norm_w, eps
+        self.norm_mode = norm_mode if q_norm_w is not None else K.QK_NORM_NONE
+        self.rotation, self.keep_first, self.sink, self.values_from_keys = rotation, keep_first, sink, values_from_keys
 
     @property
     def proj_cols(self):
-        return self.heads * self.dk + self.kv_heads * (self.dk + self.dv)
+        return self.heads * self.dk + self.kv_heads * self.dk + (0 if self.values_from_keys else self.kv_heads * self.dv)
 
     def alloc_cache(self, n_slots, n_token_slots, dtype, device):
         return {"k": torch.zeros(n_token_slots, self.kv_heads, self.dk, dtype=dtype, device=device),
                 "v": torch.zeros(n_token_slots, self.kv_heads, self.dv, dtype=dtype, device=device)}
 
     def attend(self, y, col0, batch, cache, page_size, out, out_col=0, out_scale=1.0):
-        """y holds q | k | v from column col0; writes heads * dv columns of `out` from out_col.  Keys and values of the new
-        tokens are normed and stored first.  A sequence that starts in this step with a long enough portion (batch.fresh)
-        runs on the package's prompt-attention kernels over its fresh q / k / v when they fit it (bf16, equal head sizes
-        of 64 or 128, 16-byte aligned rows); every other token — portions that continue a sequence, decoded tokens, other
-        head sizes, f32 — reads its keys from the pages."""
-        kc, vc = col0 + self.heads * self.dk, col0 + self.heads * self.dk + self.kv_heads * self.dk
-        K.qk_norm_store(y, col0, kc, vc, self.q_norm_w, self.k_norm_w, self.eps, self.heads, self.kv_heads, self.dk, self.dv,
-                        cache["k"], cache["v"], batch.slot_of_tok)
-        tok_index = None
+        """y holds q | k | v (q | k when the values are the keys) from column col0; writes heads * dv columns of `out`
+        from out_col.  Keys and values of the new tokens are normed, rotated and stored first.  A sequence that starts
+        in this step with a long enough portion (batch.fresh) runs on tensor-core prompt kernels over its fresh q / k / v
+        when they fit (bf16, equal head sizes of 64 or 128, 16-byte aligned rows); every other token — portions that
+        continue a sequence, decoded tokens, other head sizes, f32 — reads its keys from the pages."""
+        kc = col0 + self.heads * self.dk
+        vc = None if self.values_from_keys else kc + self.kv_heads * self.dk
         aligned = all(v % 8 == 0 for v in (y.stride(0), col0, out.stride(0), out_col))
-        if batch.fresh and y.dtype == torch.bfloat16 and self.dk == self.dv and self.dk in (64, 128) and aligned:
-            for row0, rows in batch.fresh:
-                K.fresh_prompt_attention(y, row0, rows, col0, kc, vc, self.heads, self.kv_heads, self.dk, self.scale, self.window, out, out_col)
-                if out_scale != 1.0:
+        fresh = bool(batch.fresh) and y.dtype == torch.bfloat16 and self.dk == self.dv and self.dk in (64, 128) and aligned
+        plain = self.sink is None and self.keep_first == 0           # the package's prompt kernels know neither
+        v_copy = torch.empty(y.shape[0], self.kv_heads * self.dk, dtype=y.dtype, device=y.device) if fresh and vc is None else None
+        cos_sin = self.rotation.table(batch) if self.rotation is not None else None
+        K.attention_prepare(y, col0, kc, vc, self.norm_mode, self.q_norm_w, self.k_norm_w, self.eps, self.heads, self.kv_heads, self.dk,
+                            self.dv, cache["k"], cache["v"], batch.slot_of_tok, cos_sin, self.rotation.dims if cos_sin is not None else 0,
+                            v_copy)
+        tok_index = None
+        if fresh:
+            vt, vcol = (y, vc) if v_copy is None else (v_copy, 0)
+            if plain and v_copy is None:
+                for row0, rows in batch.fresh:
+                    K.fresh_prompt_attention(y, row0, rows, col0, kc, vc, self.heads, self.kv_heads, self.dk, self.scale, self.window, out, out_col)
+            else:
+                K.prompt_attention(y, col0, y, kc, vt, vcol, batch.fresh_rows, len(batch.fresh), max(r for _, r in batch.fresh), self.heads,
+                                   self.kv_heads, self.dk, self.scale, self.window, self.keep_first, self.sink, out, out_col)
+            if out_scale != 1.0:
+                for row0, rows in batch.fresh:
                     K.scale_rows(out, row0, rows, out_col, self.heads * self.dv, out_scale)
             tok_index = batch.paged_tok
             if tok_index.numel() == 0:
                 return
-        K.window_attention(y, col0, cache["k"], cache["v"], self.heads, self.kv_heads, self.dk, self.dv, self.scale, self.window,
-                           batch, page_size, out, out_col, out_scale, tok_index)
+        K.paged_attention(y, col0, cache["k"], cache["v"], self.heads, self.kv_heads, self.dk, self.dv, self.scale, self.window,
+                          self.keep_first, self.sink, batch, page_size, out, out_col, out_scale, tok_index)
+
+
+class AttentionMixer:
+    """A `WindowAttention` with its own projections: one input GEMM for q | k | v (optionally biased), attention,
+    output projection (optionally biased)."""
+
+    def __init__(self, attn: WindowAttention, w_in, w_out, page_size, b_in=None, b_out=None):
+        self.attn, self.w_in, self.w_out, self.b_in, self.b_out, self.page_size = attn, w_in, w_out, b_in, b_out, page_size
+
+    def alloc_cache(self, n_slots, n_token_slots, dtype, device):
+        return self.attn.alloc_cache(n_slots, n_token_slots, dtype, device)
+
+    def forward(self, h, batch, cache):
+        y = F.linear(h, self.w_in, self.b_in)
+        o = torch.empty(h.shape[0], self.attn.heads * self.attn.dv, dtype=h.dtype, device=h.device)
+        self.attn.attend(y, 0, batch, cache, self.page_size, o)
+        return F.linear(o, self.w_out, self.b_out)
+
+
+class MatrixMemoryMixer:
+    """Stabilised matrix memory (mLSTM): per head S_t = keep_t S_(t-1) + take_t k_t v_t^T and n_t likewise with k_t alone,
+    keep / take from capped log gates and their running maximum m (from 0); y_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t))
+    + 1e-6) with q scaled by dk^(-1/2); unit RMS per head, weight, output gate sigmoid(W_g h), output projection.
+    The recurrence is the package's linear scan with per-token decay and input scale; n is the state's extra column
+    under a value that is constantly 1.  Gate pre-activations are an f32 product."""
+
+    def __init__(self, w_qkvg, w_gates, b_gates, w_o, norm_w, heads, dk, dv, cap, eps):
+        self.w_qkvg, self.w_gates, self.b_gates, self.w_o, self.norm_w = w_qkvg, w_gates, b_gates, w_o, norm_w
+        self.heads, self.dk, self.dv, self.cap, self.eps = heads, dk, dv, cap, eps
+        self.dvp = -(-(dv + 1) // 8) * 8            # values + the ones column, padded to whole 16-byte groups
+
+    def alloc_cache(self, n_slots, n_token_slots, dtype, device):
+        return {"state": torch.zeros(n_slots, self.heads, self.dk, self.dvp, dtype=torch.float32, device=device),
+                "m": torch.zeros(n_slots, self.heads, dtype=torch.float32, device=device)}
+
+    def forward(self, h, batch, cache):
+        H, dk, dv = self.heads, self.dk, self.dv
+        y = linear(h, self.w_qkvg)                                         # [T, 2 H dk + 2 H dv]: q | k | v | g
+        raw = torch.addmm(self.b_gates, h.float(), self.w_gates.t())        # [T, 2 H]: input gates | forget gates
+        keep, take, m_tok = K.mlstm_gates(raw, H, self.cap, cache["m"], batch)
+        vaug = K.append_ones(y, 2 * H * dk, H, dv, self.dvp)
+        o = K.linear_scan(y, 0, y, H * dk, vaug, 0, H, H, dk, self.dvp, cache["state"], batch, decay_tok=keep, scale_tok=take)
+        on = K.mlstm_out_norm(o, self.dvp, m_tok, dk ** -0.5, y, 2 * H * dk + H * dv, self.norm_w, self.eps, H, dv, h.dtype)
+        return linear(on, self.w_o)
 
 
 class StateSpaceMixer:
@@ -149,18 +255,44 @@ class DenseGLU:
         return linear(K.glu_split(linear(h, self.w_gate_up), self.act), self.w_down)
 
 
+class DenseMLP:
+    """down(act(up h)): a feed-forward without a gate."""
+
+    def __init__(self, w_up, w_down, act):
+        self.w_up, self.w_down, self.act = w_up, w_down, act
+
+    def hidden(self, h):
+        u = linear(h, self.w_up)
+        K.activate_cols(u, 0, u.shape[1], self.act)
+        return u
+
+    def forward(self, h):
+        return linear(self.hidden(h), self.w_down)
+
+    def forward_added_to(self, h, other):
+        """other + down(act(up h)): the sum forms in the product's f32 accumulator."""
+        return torch.addmm(other, self.hidden(h), self.w_down.t())
+
+
 class RoutedExperts:
-    """Softmax router in f32 with a choice-only bias and group-limited top-k; experts are GLU feed-forwards.  Few
-    (token, expert) pairs: two weight-streaming kernels.  Many: rows sorted by expert, one GEMM pair per expert that
-    has rows (the per-expert row counts cross to the host once per layer), weighted combine in f32."""
+    """Router logits in f32.  Rule "grouped_softmax": softmax over all experts, a choice-only bias, group-limited top-k,
+    weights = the scores (optionally renormalised).  Rule "top_softmax": the largest logits, weights = softmax over the
+    chosen logits alone.  Experts are GLU feed-forwards (`gated`: w_up holds gate | up rows) or plain down(act(up h)); a
+    `shared` feed-forward, when given, runs for every token and is added.  Few (token, expert) pairs: two
+    weight-streaming kernels.  Many: rows sorted by expert, one GEMM pair per expert that has rows (the per-expert row
+    counts cross to the host once per layer), weighted combine in f32."""
 
     # Up to this many (token, expert) pairs per expert the weights are simply streamed once per pair: 4 while an expert is
     # small enough that repeated reads hit L2, 2 above that.
     SMALL_EXPERT_BYTES = 32 << 20
 
-    def __init__(self, w_router, correction, w_gate_up, w_down, top, n_groups, keep_groups, act, renorm=False):
+    def __init__(self, w_router, correction, w_gate_up, w_down, top, n_groups, keep_groups, act, renorm=False, rule="grouped_softmax",
+                 gated=True, shared=None):
+        if rule not in ("grouped_softmax", "top_softmax"):
+            raise ValueError(f"unknown routing rule {rule!r}")
         self.w_router, self.correction, self.w_gate_up, self.w_down = w_router, correction, w_gate_up, w_down
         self.top, self.n_groups, self.keep_groups, self.act, self.renorm = top, n_groups, keep_groups, act, renorm
+        self.rule, self.gated, self.shared = rule, gated, shared
         self.n_experts = w_gate_up.shape[0]
 
     def streams_weights(self, n_tok):
@@ -170,19 +302,28 @@ class RoutedExperts:
 
     def route(self, h):
         logits = F.linear(h.float(), self.w_router)
+        if self.rule == "top_softmax":
+            return K.moe_route_top_softmax(logits, self.top)
         return K.moe_route(logits, self.correction, self.n_groups, self.keep_groups, self.top, self.renorm)
 
     def forward(self, h):
         experts, weights = self.route(h)
         if self.streams_weights(h.shape[0]):
-            return K.moe_small(h, self.w_gate_up, self.w_down, experts, weights, self.act)
-        counts, order = K.moe_sort(experts, self.n_experts)
-        xs = K.moe_gather(h, order, self.top)
-        ys = torch.empty_like(xs)
-        at = 0
-        for e, n in enumerate(counts.tolist()):
-            if n:
-                hid = K.glu_split(linear(xs[at:at + n], self.w_gate_up[e]), self.act)
-                torch.mm(hid, self.w_down[e].t(), out=ys[at:at + n])
-                at += n
-        return K.moe_combine(ys, order, weights)
+            small = K.moe_small if self.gated else K.moe_small_ungated
+            out = small(h, self.w_gate_up, self.w_down, experts, weights, self.act)
+        else:
+            counts, order = K.moe_sort(experts, self.n_experts)
+            xs = K.moe_gather(h, order, self.top)
+            ys = torch.empty_like(xs)
+            at = 0
+            for e, n in enumerate(counts.tolist()):
+                if n:
+                    hid = linear(xs[at:at + n], self.w_gate_up[e])
+                    if self.gated:
+                        hid = K.glu_split(hid, self.act)
+                    else:
+                        K.activate_cols(hid, 0, hid.shape[1], self.act)
+                    torch.mm(hid, self.w_down[e].t(), out=ys[at:at + n])
+                    at += n
+            out = K.moe_combine(ys, order, weights)
+        return out if self.shared is None else self.shared.forward_added_to(h, out)

@@ -39,6 +39,11 @@ def _load_nisasun(model_dir, device, dtype, **options):
     return NisasunModel.from_dir(model_dir, device, dtype, **options)
 
 
+def _load_kilizen(model_dir, device, dtype, **options):
+    from .kilizen import KilizenModel
+    return KilizenModel.from_dir(model_dir, device, dtype, **options)
+
+
 def _load_llama(model_dir, device, dtype, **options):
     """Llama-family UQFF folder (config.json + *.uqff shards + residual.safetensors) -> `model.LlamaWeights`, the object
     `model.LlamaRunner` / `model.LlamaPrefill` drive."""
@@ -54,5 +59,6 @@ def _load_llama(model_dir, device, dtype, **options):
 
 
 register("Nisasun", _load_nisasun)
+register("Kilizen", _load_kilizen)
 for _name in ("LlamaForCausalLM", "MistralForCausalLM", "llama", "mistral"):
     register(_name, _load_llama)

@@ -12,7 +12,8 @@ from . import ExtensionMissing
 _HERE = os.path.dirname(os.path.abspath(__file__))
 SEQ_LIB_PATH = os.path.join(_HERE, "libmrs_b200_seq.so")
 BF16, F32 = 1, 2
-ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID = 0, 1, 2, 3
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID, ACT_GELU_ERF, ACT_RELU_SQ = 0, 1, 2, 3, 4, 5
+QK_NORM_NONE, QK_NORM_HEAD, QK_NORM_WHOLE = 0, 1, 2
 DTYPE_CODE = {torch.bfloat16: BF16, torch.float32: F32}
 _lib = None
 
@@ -51,6 +52,25 @@ class ScanArgs(ctypes.Structure):
                 ("cu_tok", ctypes.c_void_p), ("past", ctypes.c_void_p), ("slot", ctypes.c_void_p),
                 ("n_seq", ctypes.c_int), ("n_tok", ctypes.c_int), ("out", ctypes.c_void_p),
                 ("seg_state", ctypes.c_void_p), ("seg_decay", ctypes.c_void_p), ("seg_len", ctypes.c_int), ("n_segs", ctypes.c_int)]
+
+class AttnPrepareArgs(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("v_copy", ctypes.c_void_p),
+                ("q_ld", ctypes.c_int64), ("k_ld", ctypes.c_int64), ("v_ld", ctypes.c_int64), ("v_copy_ld", ctypes.c_int64),
+                ("dtype", ctypes.c_int), ("norm_mode", ctypes.c_int),
+                ("q_norm_w", ctypes.c_void_p), ("k_norm_w", ctypes.c_void_p), ("eps", ctypes.c_float),
+                ("heads", ctypes.c_int), ("kv_heads", ctypes.c_int), ("dk", ctypes.c_int), ("dv", ctypes.c_int),
+                ("rot_dims", ctypes.c_int), ("cos_sin", ctypes.c_void_p),
+                ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p), ("slot_of_tok", ctypes.c_void_p), ("n_tok", ctypes.c_int)]
+
+
+class PagedAttentionArgs(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("q_ld", ctypes.c_int64), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("dtype", ctypes.c_int), ("heads", ctypes.c_int), ("kv_heads", ctypes.c_int), ("dk", ctypes.c_int), ("dv", ctypes.c_int),
+                ("scale", ctypes.c_float), ("window", ctypes.c_int), ("keep_first", ctypes.c_int), ("sink", ctypes.c_void_p),
+                ("pages", ctypes.c_void_p), ("pages_ld", ctypes.c_int), ("page_size", ctypes.c_int),
+                ("seq_of_tok", ctypes.c_void_p), ("pos_of_tok", ctypes.c_void_p), ("tok_index", ctypes.c_void_p), ("n_tok", ctypes.c_int),
+                ("out", ctypes.c_void_p), ("out_ld", ctypes.c_int64), ("out_scale", ctypes.c_float)]
+
 
 SCAN_SEGMENT = 256                  # tokens per segment when a long portion is scanned as segments side by side
 SCAN_SEGMENT_MIN_TOKENS = 1024      # portions shorter than this run in one pass
@@ -259,4 +279,127 @@ def moe_combine(sorted_y, order, weights):
     out = torch.empty(T, W, dtype=sorted_y.dtype, device=sorted_y.device)
     _ok(lib().mrs_seq_moe_combine(_p(sorted_y), _i(DTYPE_CODE[sorted_y.dtype]), _p(order), _p(weights), _i(T), _i(top), _i(W),
                                   _p(inverse), _p(out), _st(sorted_y)), "moe_combine")
+    return out
+
+
+# ---- single residual with Dynamic Tanh norms ------------------------------------------------------------
+def tanh_norm_rows(x, norm, dtype, rows=None):
+    """dyt(x[rows]) for the f32 residual x [T, W]; norm = (alpha, weight, bias) f32 on the device."""
+    T, W = x.shape
+    n = T if rows is None else rows.numel()
+    out = torch.empty(n, W, dtype=dtype, device=x.device)
+    _ok(lib().mrs_seq_tanh_norm_rows(_p(x), _p(rows), _p(norm[0]), _p(norm[1]), _p(norm[2]), _p(out), _i(DTYPE_CODE[dtype]), _i(n), _i(W),
+                                     _st(x)), "tanh_norm_rows")
+    return out
+
+
+def residual_tanh_norm(x, y=None, post=None, extra=None, nxt=None, dtype=None):
+    """In place on the f32 residual: x += dyt_post(y); x += extra; returns dyt_next(x) when nxt is given (each part optional)."""
+    T, W = x.shape
+    dtype = y.dtype if y is not None else dtype
+    out = torch.empty(T, W, dtype=dtype, device=x.device) if nxt is not None else None
+    post, nxt = post or (None, None, None), nxt or (None, None, None)
+    _ok(lib().mrs_seq_residual_tanh_norm(_p(x), _p(y), _i(DTYPE_CODE[dtype]), _p(post[0]), _p(post[1]), _p(post[2]), _p(extra), _p(nxt[0]),
+                                         _p(nxt[1]), _p(nxt[2]), _p(out), _i(T), _i(W), _st(x)), "residual_tanh_norm")
+    return out
+
+
+# ---- attention: general preparation, rotation table, sink / kept-first window ---------------------------
+def rotation_table(pos_of_tok, freq, mag):
+    """f32 [T, half, 2]: mag * (cos, sin)(pos * freq), angles in double.  freq: f64 on the device."""
+    T, half = pos_of_tok.numel(), freq.numel()
+    out = torch.empty(T, half, 2, dtype=torch.float32, device=freq.device)
+    _ok(lib().mrs_seq_rotation_table(_p(pos_of_tok), _p(freq), _i(T), _i(half), _f(mag), _p(out), _st(freq)), "rotation_table")
+    return out
+
+
+def attention_prepare(y, q_col, k_col, v_col, norm_mode, q_norm_w, k_norm_w, eps, heads, kv_heads, dk, dv, k_cache, v_cache, slot_of_tok,
+                      cos_sin=None, rot_dims=0, v_copy=None):
+    """q | k | v are column ranges of y.  v_col None: the values are the keys as projected; v_copy [T, kv_heads * dk], when
+    given, also receives them."""
+    a = AttnPrepareArgs()
+    ld = y.stride(0)
+    a.q, a.k, a.q_ld, a.k_ld = _p(y, q_col).value, _p(y, k_col).value, ld, ld
+    if v_col is not None:
+        a.v, a.v_ld = _p(y, v_col).value, ld
+    elif v_copy is not None:
+        a.v_copy, a.v_copy_ld = v_copy.data_ptr(), v_copy.stride(0)
+    a.dtype, a.norm_mode = DTYPE_CODE[y.dtype], norm_mode
+    a.q_norm_w, a.k_norm_w, a.eps = _p(q_norm_w).value, _p(k_norm_w).value, eps
+    a.heads, a.kv_heads, a.dk, a.dv = heads, kv_heads, dk, dv
+    a.rot_dims, a.cos_sin = rot_dims, _p(cos_sin).value
+    a.k_cache, a.v_cache, a.slot_of_tok, a.n_tok = k_cache.data_ptr(), v_cache.data_ptr(), slot_of_tok.data_ptr(), y.shape[0]
+    _ok(lib().mrs_seq_attention_prepare(ctypes.byref(a), _st(y)), "attention_prepare")
+
+
+def paged_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, window, keep_first, sink, batch, page_size, out, out_col=0,
+                    out_scale=1.0, tok_index=None):
+    """Every token of the step (or those listed in tok_index) against the pages of its sequence: position i sees j <= i
+    with i - j < window (0: all) or j < keep_first; sink [heads] f32 or None."""
+    a = PagedAttentionArgs()
+    a.q, a.q_ld, a.k_cache, a.v_cache = _p(y, q_col).value, y.stride(0), k_cache.data_ptr(), v_cache.data_ptr()
+    a.dtype, a.heads, a.kv_heads, a.dk, a.dv = DTYPE_CODE[y.dtype], heads, kv_heads, dk, dv
+    a.scale, a.window, a.keep_first, a.sink = scale, int(window), int(keep_first), _p(sink).value
+    a.pages, a.pages_ld, a.page_size = batch.pages.data_ptr(), batch.pages.shape[1], page_size
+    a.seq_of_tok, a.pos_of_tok, a.tok_index = batch.seq_of_tok.data_ptr(), batch.pos_of_tok.data_ptr(), _p(tok_index).value
+    a.n_tok = y.shape[0] if tok_index is None else tok_index.numel()
+    a.out, a.out_ld, a.out_scale = _p(out, out_col).value, out.stride(0), out_scale
+    _ok(lib().mrs_seq_paged_attention(ctypes.byref(a), _st(y)), "paged_attention")
+
+
+def prompt_attention(q, q_col, k, k_col, v, v_col, seq_rows, n_seq, longest, heads, kv_heads, d, scale, window, keep_first, sink, out,
+                     out_col=0):
+    """Sequences that start in this step, over their own fresh rows (bf16, head size 64 or 128) on tensor cores.
+    seq_rows i32 [n_seq, 2]: first row and row count of every such sequence; q / k / v: column ranges of 2-D tensors."""
+    _ok(lib().mrs_seq_prompt_attention(_p(q, q_col), _p(k, k_col), _p(v, v_col), _p(out, out_col), _p(seq_rows), _i(n_seq), _i(longest),
+                                       _i(heads), _i(kv_heads), _i(d), _l(q.stride(0)), _l(k.stride(0)), _l(v.stride(0)), _l(out.stride(0)),
+                                       _f(scale), _i(int(window)), _i(int(keep_first)), _p(sink), _st(q)), "prompt_attention")
+
+
+# ---- stabilised matrix memory ---------------------------------------------------------------------------
+def mlstm_gates(raw, heads, cap, m_state, batch):
+    """raw f32 [T, 2 * heads] (input gates | forget gates, biases added) -> keep, take, m f32 [T, heads]; advances m_state."""
+    T = raw.shape[0]
+    keep = torch.empty(T, heads, dtype=torch.float32, device=raw.device)
+    take, m_tok = torch.empty_like(keep), torch.empty_like(keep)
+    _ok(lib().mrs_seq_mlstm_gates(_p(raw), _p(raw, heads), _l(raw.stride(0)), _f(cap), _i(heads), _p(m_state), _p(batch.cu_tok),
+                                  _p(batch.past), _p(batch.slot), _i(batch.n_seq), _i(T), _p(keep), _p(take), _p(m_tok), _st(raw)),
+        "mlstm_gates")
+    return keep, take, m_tok
+
+
+def append_ones(y, v_col, heads, dv, dvp):
+    out = torch.empty(y.shape[0], heads * dvp, dtype=y.dtype, device=y.device)
+    _ok(lib().mrs_seq_append_ones(_p(y, v_col), _l(y.stride(0)), _i(DTYPE_CODE[y.dtype]), _i(heads), _i(dv), _i(dvp), _i(y.shape[0]), _p(out),
+                                  _st(y)), "append_ones")
+    return out
+
+
+def mlstm_out_norm(o, dvp, m_tok, q_scale, gate, gate_col, weight, eps, heads, dv, dtype):
+    T = o.shape[0]
+    out = torch.empty(T, heads * dv, dtype=dtype, device=o.device)
+    _ok(lib().mrs_seq_mlstm_out_norm(_p(o), _i(dvp), _p(m_tok), _f(q_scale), _p(gate, gate_col), _l(gate.stride(0)), _p(weight), _f(eps),
+                                     _i(heads), _i(dv), _p(out), _l(out.stride(0)), _i(DTYPE_CODE[dtype]), _i(T), _st(o)), "mlstm_out_norm")
+    return out
+
+
+# ---- experts: plain top-k rule, experts without a gate -----------------------------------------------------
+def moe_route_top_softmax(logits, top):
+    T, E = logits.shape
+    experts = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    _ok(lib().mrs_seq_moe_route_top_softmax(_p(logits), _i(T), _i(E), _i(top), _p(experts), _p(weights), _st(logits)), "moe_route_top_softmax")
+    return experts, weights
+
+
+def moe_small_ungated(x, up, down, experts, weights, act):
+    """Expert feed-forward without a gate by weight streaming (few tokens): up [E, ff, W], down [E, W, ff]."""
+    T, W = x.shape
+    top, ff = experts.shape[1], down.shape[2]
+    code = _i(DTYPE_CODE[x.dtype])
+    hidden = torch.empty(T * top, ff, dtype=x.dtype, device=x.device)
+    out = torch.empty(T, W, dtype=x.dtype, device=x.device)
+    _ok(lib().mrs_seq_moe_up(_p(x), _p(up), code, _p(experts), _i(T), _i(top), _i(W), _i(ff), _i(act), _p(hidden), _st(x)), "moe_up")
+    _ok(lib().mrs_seq_moe_down(_p(hidden), _p(down), code, _p(experts), _p(weights), _i(T), _i(top), _i(W), _i(ff), _p(out), _st(x)),
+        "moe_down")
     return out
