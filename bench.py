@@ -484,7 +484,7 @@ def bench_nisasun(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
             setattr(mod, name, g)
             return f
         names = ["embed_streams", "streams_read_norm", "streams_write", "glu_split", "gated_group_norm", "causal_conv", "ssm_steps",
-                 "linear_scan", "qk_norm_store", "window_attention", "fresh_prompt_attention", "scale_rows", "activate_cols", "moe_route", "moe_small", "moe_sort", "moe_gather", "moe_combine"]
+                 "linear_scan", "attention_prepare", "paged_attention", "fresh_prompt_attention", "scale_rows", "activate_cols", "moe_route", "moe_small", "moe_sort", "moe_gather", "moe_combine"]
         saved = {n: wrap(K, n) for n in names}
         saved_lin = wrap(mixers, "linear")
 
@@ -530,7 +530,7 @@ def bench_nisasun(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
                                "tflops_f32": scan_flop / (ops["linear_scan"] * 1e-3) / 1e12}
         win = L["mask"]["size"]
         attn_flop = n_par * 2.0 * L["heads"] * (L["dim"] + L["vdim"]) * sum(min(i + 1, win) for i in range(prompt))
-        attn_ms = ops.get("fresh_prompt_attention", 0.0) + ops.get("window_attention", 0.0) + ops.get("scale_rows", 0.0)
+        attn_ms = ops.get("fresh_prompt_attention", 0.0) + ops.get("paged_attention", 0.0) + ops.get("scale_rows", 0.0)
         roof["window_attention (prompt)"] = {"ms": attn_ms, "tflops": attn_flop / (attn_ms * 1e-3) / 1e12,
                                              "tensor_frac": attn_flop / (attn_ms * 1e-3) / 1e12 / tpeak,
                                              "kernel": "prompt-attention kernels over fresh q/k/v" if "fresh_prompt_attention" in ops else "paged kernel"}
@@ -585,6 +585,177 @@ def bench_nisasun(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
                                  "at context %d; L2 flushed between repetitions" % (list(widths), prompt, prompt // 8)}
     return out
 
+# ------------------------------------------------------------------------------------------- --arch kilizen
+def kilizen_bench_config(width, vocab=32000):
+    """Four layers, one of each kind of mixer and feed-forward, at sizes of a real model's layers of this width."""
+    H = width // 128
+    rot = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+    win = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot, "mask": {"size": 1024, "keep_first": 64}}
+    full = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 128}}
+    mem = {"heads": H, "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    dense = {"kind": "dense", "ff": 4 * width}
+    moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 16, "top": 2}, "shared": {"ff": width}}
+    return {"architecture": "Kilizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention_2", "mixer": full, "mlp": dense}, {"type": "mlstm", "mixer": mem, "mlp": moe},
+                       {"type": "attention", "mixer": win, "mlp": dense}, {"type": "mlstm", "mixer": mem, "mlp": moe}]}
+
+
+def bench_kilizen(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), prompt=4096, decode_batches=(1, 32)):
+    """Prefill and decode throughput of the Kilizen design through `engine.Engine.execute` at layer sizes of a real model,
+    and of the Nisasun design (the closest model: same engine, same kernel library) at equal width / depth / head and
+    feed-forward sizes; then, per kernel, the achieved fraction of the measured HBM rate (or f32 / tensor TFLOP/s) beside
+    the like kernel of Nisasun.  CUDA events, L2 flushed between repetitions."""
+    import numpy as np
+    from mistralrs_b200 import engine, kilizen, mixers, nisasun, seq_ops as K
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    tpeak = peaks.get("bf16_tflops_sustained", 1400.0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    warmup, steps = max(3, warmup), max(1, steps)
+    names = [n for n in ("embed_streams", "streams_read_norm", "streams_write", "glu_split", "gated_group_norm", "causal_conv", "ssm_steps", "linear_scan",
+                         "qk_norm_store", "window_attention", "fresh_prompt_attention", "scale_rows", "activate_cols", "moe_route", "moe_small", "moe_sort",
+                         "moe_gather", "moe_combine", "tanh_norm_rows", "residual_tanh_norm", "rotation_table", "attention_prepare", "paged_attention",
+                         "prompt_attention", "mlstm_gates", "append_ones", "mlstm_out_norm", "moe_route_top_softmax", "moe_small_ungated")]
+
+    def timed(fn, reps=steps):
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        return sorted(ts)[len(ts) // 2]
+
+    def by_op(fn):
+        """One call of fn with CUDA events around every kernel wrapper and every library GEMM of the mixers."""
+        acc, saved = {}, {}
+
+        def wrap(mod, name):
+            f = getattr(mod, name)
+
+            def g(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = f(*a, **k)
+                e1.record()
+                acc.setdefault(name, []).append((e0, e1))
+                return r
+            setattr(mod, name, g)
+            saved[(mod, name)] = f
+        for n in names:
+            wrap(K, n)
+        wrap(mixers, "linear")
+        try:
+            torch.cuda.synchronize()
+            flush.zero_()
+            fn()
+            torch.cuda.synchronize()
+        finally:
+            for (mod, name), f in saved.items():
+                setattr(mod, name, f)
+        return {n: round(sum(a.elapsed_time(b) for a, b in v), 4) for n, v in acc.items()}
+
+    def measure(model, vocab, rng):
+        row = {}
+        eng = engine.Engine(model, max_tokens=max(prompt, 32 * (prompt // 8 + 64)) + 64, max_seqs=max(decode_batches))
+        toks = rng.integers(0, vocab, prompt).tolist()
+
+        def prefill():
+            r = eng.new_request(toks)
+            eng.execute([(r, prompt)])
+            eng.finish(r)
+        t = timed(prefill)
+        row["prefill_tok_s"], row["prefill_ms"] = prompt / t, t * 1e3
+        row["prefill_ms_by_op"] = by_op(prefill)
+        row["decode"] = []
+        ctx = prompt // 8
+        for b in decode_batches:
+            reqs = [eng.new_request(rng.integers(0, vocab, ctx + 64).tolist()) for _ in range(b)]
+            eng.execute([(r, ctx) for r in reqs])
+
+            def dec():
+                eng.execute([(r, 1) for r in reqs])
+            t = timed(dec, reps=max(steps, 5))
+            eng.decode_graphs, graphs = False, eng.decode_graphs          # the per-op table needs the eager step
+            ops = by_op(dec)
+            eng.decode_graphs = graphs
+            row["decode"].append({"batch": b, "context": ctx, "tok_s": b / t, "ms_per_step": t * 1e3, "graph": b in eng._graphs, "ms_by_op": ops})
+            for r in reqs:
+                eng.finish(r)
+        del eng
+        torch.cuda.empty_cache()
+        return row
+
+    out = {"metric": "kilizen_prefill_tok_s", "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True,
+           "dtype": "bf16 (f32 residual, states, gates, norms, softmax, router)", "data": "synthetic", "sizes": []}
+    for width in widths:
+        rng = np.random.default_rng(width)
+        cj = kilizen_bench_config(width)
+        cfg = kilizen.KilizenConfig(cj)
+        model = kilizen.KilizenModel.random(cfg, dev, torch.bfloat16, seed=width)
+        row = {"width": width, "layers": len(cj["layers"]), "prompt_tokens": prompt}
+        row.update(measure(model, cfg.vocab, rng))
+        del model
+        torch.cuda.empty_cache()
+        ncj = nisasun_bench_config(width)
+        ncfg = nisasun.NisasunConfig(ncj)
+        nmodel = nisasun.NisasunModel.random(ncfg, dev, torch.bfloat16, seed=width)
+        row["nisasun_equal_size"] = near = measure(nmodel, ncfg.vocab, rng)
+        del nmodel
+        torch.cuda.empty_cache()
+        # ---- per kernel: achieved rate on the algorithmic bytes / flops of the prefill, beside the like kernel ----
+        T, W, H, d = prompt, width, width // 128, 128
+        G, ops, nops = max(1, H // 4), row["prefill_ms_by_op"], near["prefill_ms_by_op"]
+        gbs = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9 / hbm if ms else None
+        tfl = lambda flop, ms: flop / (ms * 1e-3) / 1e12 if ms else None
+        roof = {}
+        # residual pass: x read + written (f32), y read, next input written (bf16); 8 sublayers, one pass without a next input
+        roof["residual_tanh_norm"] = {"ms": ops.get("residual_tanh_norm"), "hbm_frac": gbs(8 * T * W * (4 + 4 + 2 + 2) - T * W * 2, ops.get("residual_tanh_norm")),
+                                      "like": "streams_write", "like_hbm_frac": gbs(8 * T * W * (2 * 4 * 2 + 2 + 2), nops.get("streams_write"))}
+        # q / k preparation: q and k read + written, k and v written to pages (+ the copy of the unnormed keys); two attention layers
+        prep = 2 * T * 2 * (2 * H * d + 2 * G * d + 2 * G * d) + T * 2 * G * d * 2
+        roof["attention_prepare"] = {"ms": ops.get("attention_prepare"), "hbm_frac": gbs(prep, ops.get("attention_prepare")),
+                                     "like": "attention_prepare (per-head norm, no rotation)", "like_hbm_frac": gbs(2 * T * 2 * (2 * H * d + 2 * G * d + 2 * G * d), nops.get("attention_prepare"))}
+        win, keep = cj["layers"][2]["mixer"]["mask"]["size"], cj["layers"][2]["mixer"]["mask"]["keep_first"]
+        seen_win = sum(min(i + 1, win) + min(keep, max(0, i + 1 - win)) for i in range(T))
+        flop_full, flop_win = 4.0 * H * d * T * (T + 1) / 2, 4.0 * H * d * seen_win
+        nwin = ncj["layers"][2]["mixer"]["left"]["mask"]["size"]
+        nflop = 2 * 4.0 * H * d * sum(min(i + 1, nwin) for i in range(T))
+        nms = nops.get("fresh_prompt_attention", 0.0) + nops.get("scale_rows", 0.0)
+        roof["prompt_attention"] = {"ms": ops.get("prompt_attention"), "tflops": tfl(flop_full + flop_win, ops.get("prompt_attention")),
+                                    "tensor_frac": (tfl(flop_full + flop_win, ops.get("prompt_attention")) or 0.0) / tpeak,
+                                    "like": "fresh_prompt_attention (+ scale_rows)", "like_tflops": tfl(nflop, nms), "like_tensor_frac": (tfl(nflop, nms) or 0.0) / tpeak}
+        dvp = -(-(d + 1) // 8) * 8
+        scan_flop = 2 * T * H * 4.0 * d * dvp
+        R = ncj["layers"][2]["mixer"]["right"]
+        nscan = 2 * T * H * 4.0 * d * d + 2 * T * R["heads"] * 4.0 * R["state"] * R["vdim"]
+        roof["linear_scan"] = {"ms": ops.get("linear_scan"), "tflops_f32": tfl(scan_flop, ops.get("linear_scan")),
+                               "like": "linear_scan", "like_tflops_f32": tfl(nscan, nops.get("linear_scan"))}
+        # output stage of the recurrence: o read (f32), gate read, result written (bf16)
+        roof["mlstm_out_norm"] = {"ms": ops.get("mlstm_out_norm"), "hbm_frac": gbs(2 * T * H * (dvp * 4 + d * 2 + d * 2), ops.get("mlstm_out_norm")),
+                                  "like": "gated_group_norm", "like_hbm_frac": gbs(2 * T * H * d * (4 + 2 + 2) + 2 * T * R["heads"] * R["vdim"] * (4 + 2 + 2),
+                                                                                nops.get("gated_group_norm"))}
+        roof["mlstm_gates + append_ones"] = {"ms": (ops.get("mlstm_gates", 0.0) + ops.get("append_ones", 0.0)),
+                                             "hbm_frac": gbs(2 * T * (H * 5 * 4 + H * d * 2 + H * dvp * 2), ops.get("mlstm_gates", 0.0) + ops.get("append_ones", 0.0)),
+                                             "like": "ssm_steps + causal_conv", "like_ms": nops.get("ssm_steps", 0.0) + nops.get("causal_conv", 0.0)}
+        roof["linear (cuBLAS)"] = {"ms": ops.get("linear"), "like_ms": nops.get("linear")}
+        dk = row["decode"][0]["ms_by_op"], near["decode"][0]["ms_by_op"]
+        ctx = prompt // 8
+        kv = lambda c: 2 * G * d * 2 * c                                           # bytes of keys + values one query head group reads per token
+        roof["paged_attention (decode, b=1)"] = {"ms": dk[0].get("paged_attention"), "hbm_frac": gbs(kv(ctx) + kv(min(ctx, win)), dk[0].get("paged_attention")),
+                                                 "like": "paged_attention", "like_hbm_frac": gbs(2 * kv(min(ctx, nwin)), dk[1].get("paged_attention"))}
+        row["roofline"] = roof
+        out["sizes"].append(row)
+    out["value"] = out["sizes"][0]["prefill_tok_s"]
+    out["ms_per_step"] = out["sizes"][0]["prefill_ms"]
+    out["config"] = {"workload": "4 layers (attention_2+dense, mlstm+moe, attention+dense, mlstm+moe), widths %s, %d-token prompt; decode at "
+                                 "context %d; Nisasun at equal sizes beside it; L2 flushed between repetitions" % (list(widths), prompt, prompt // 8)}
+    return out
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -595,9 +766,10 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="headline workload: 1 = TinyLlama-1.1B Q4_K_M on the CPU (plumbing, no GPU), 2 = 8B Q4_K_M decode b=1 (default), "
                          "3 = 8B Q8_0 prefill 4096, 4 = Mistral-7B GPTQ b=32, 5 = Llama-3-70B Q4_K_M tensor parallel (needs --gpus 8)")
-    ap.add_argument("--arch", default="llama", choices=["llama", "nisasun"],
+    ap.add_argument("--arch", default="llama", choices=["llama", "nisasun", "kilizen"],
                     help="nisasun: prefill / decode throughput of the Nisasun design on the step engine at layer sizes of a real model "
-                         "(random weights), beside the Llama path at equal width / depth / feed-forward size, with a per-kernel table")
+                         "(random weights), beside the Llama path at equal width / depth / feed-forward size, with a per-kernel table; "
+                         "kilizen: the same for the Kilizen design, beside Nisasun at equal sizes")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model")
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("MRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -634,6 +806,9 @@ def main():
 
     if args.arch == "nisasun":
         print(json.dumps(bench_nisasun(torch, dev, peaks, steps=args.steps, warmup=args.warmup)))
+        return
+    if args.arch == "kilizen":
+        print(json.dumps(bench_kilizen(torch, dev, peaks, steps=args.steps, warmup=args.warmup)))
         return
     if args.config == 3 and world == 1:
         pf = bench_prefill_q8(M, torch, dev, peaks, layers=args.layers)

@@ -6,7 +6,7 @@
 //
 // The recurrence itself is mrs_seq_linear_scan with per-token decay and input scale; the normaliser n rides along as
 // one more value column that is constantly 1.  Here: the gate kernel (soft cap, log-sigmoid, the running maximum as a
-// warp scan over 32 tokens at a time, carried per sequence), the ones column, and the output stage (denominator, unit
+// scan over blocks of 32 tokens side by side, carried per sequence), the ones column, and the output stage (denominator, unit
 // RMS per head, weight, sigmoid gate).  Everything is f32 except the value copy and the gate / output activations.
 #include "seq_common.cuh"
 
@@ -15,24 +15,25 @@ namespace seq {
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float soft_cap_f(float z, float cap) { return cap > 0.0f ? cap * tanhf(z / cap) : z; }
 
-// one warp per (sequence, head).  Inside a block of 32 tokens with inclusive prefix sums F of f:
-//   m_l = F_l + max(m_start, max_{j <= l}(i_j - F_j))
-// which equals the token-by-token rule; keep / take are then formed from the m values actually stored, so they stay
-// consistent with them whatever the rounding of the scan.
-__global__ void mlstm_gates_kernel(const float *__restrict__ raw_in, const float *__restrict__ raw_forget, int64_t raw_ld, float cap, int heads,
-                                   float *__restrict__ m_state, const int32_t *__restrict__ cu_tok, const int32_t *__restrict__ past,
-                                   const int32_t *__restrict__ slot, int n_seq, float *__restrict__ keep, float *__restrict__ take,
-                                   float *__restrict__ m_tok) {
-  const int lane = threadIdx.x & 31;
-  const int job = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (job >= n_seq * heads) return;
-  const int b = job / heads, h = job % heads;
+// One CTA of GATE_WARPS warps per (sequence, head); every warp takes a block of 32 tokens, GATE_WARPS blocks per round.
+// Inside a block with inclusive prefix sums F of f:  m_l = F_l + max(m_start, max_{j <= l}(i_j - F_j)), which equals the
+// token-by-token rule; a block's effect on the running maximum is the pair (F_31, max_j(i_j - F_j)), so the warps compute
+// their blocks side by side and then fold the pairs of the blocks before theirs.  keep / take are formed from the m
+// values actually stored, so they stay consistent with them whatever the rounding of the scan.
+constexpr int GATE_WARPS = 8;
+__global__ void __launch_bounds__(GATE_WARPS * 32) mlstm_gates_kernel(const float *__restrict__ raw_in, const float *__restrict__ raw_forget, int64_t raw_ld,
+                                   float cap, int heads, float *__restrict__ m_state, const int32_t *__restrict__ cu_tok,
+                                   const int32_t *__restrict__ past, const int32_t *__restrict__ slot, float *__restrict__ keep,
+                                   float *__restrict__ take, float *__restrict__ m_tok) {
+  __shared__ float tot_f[GATE_WARPS], top_g[GATE_WARPS];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int b = blockIdx.x / heads, h = blockIdx.x % heads;
   const int t_begin = cu_tok[b], t_end = cu_tok[b + 1];
   if (t_end <= t_begin) return;
   float *ms = m_state + (int64_t)slot[b] * heads + h;
-  float m_start = past[b] > 0 ? *ms : 0.0f;
-  for (int t0 = t_begin; t0 < t_end; t0 += 32) {
-    const int t = t0 + lane;
+  float m_round = past[b] > 0 ? *ms : 0.0f;          // the running maximum before this round
+  for (int r0 = t_begin; r0 < t_end; r0 += GATE_WARPS * 32) {
+    const int t = r0 + wib * 32 + lane;
     const bool live = t < t_end;
     const float f = live ? log_sigmoid_f(soft_cap_f(raw_forget[(int64_t)t * raw_ld + h], cap)) : 0.0f;
     const float i = live ? soft_cap_f(raw_in[(int64_t)t * raw_ld + h], cap) : -INFINITY;
@@ -48,6 +49,10 @@ __global__ void mlstm_gates_kernel(const float *__restrict__ raw_in, const float
       const float o = __shfl_up_sync(0xffffffffu, G, d);
       if (lane >= d) G = fmaxf(G, o);
     }
+    if (lane == 31) { tot_f[wib] = F; top_g[wib] = G; }
+    __syncthreads();
+    float m_start = m_round;                          // fold the blocks before this warp's (a dead block: F = 0, G = -inf)
+    for (int w = 0; w < wib; w++) m_start = tot_f[w] + fmaxf(m_start, top_g[w]);
     const float m = F + fmaxf(m_start, G);
     float before = __shfl_up_sync(0xffffffffu, m, 1);
     if (lane == 0) before = m_start;
@@ -57,9 +62,11 @@ __global__ void mlstm_gates_kernel(const float *__restrict__ raw_in, const float
       take[at] = expf(i - m);
       m_tok[at] = m;
     }
-    m_start = __shfl_sync(0xffffffffu, m, 31);   // lanes past the end repeat the last live value (f = 0, i = -inf)
+    for (int w = wib; w < GATE_WARPS; w++) m_start = tot_f[w] + fmaxf(m_start, top_g[w]);
+    m_round = m_start;                                // every warp arrives at the same value
+    __syncthreads();
   }
-  if (lane == 0) *ms = m_start;
+  if (threadIdx.x == 0) *ms = m_round;
 }
 
 template <typename T>
@@ -104,9 +111,8 @@ extern "C" int mrs_seq_mlstm_gates(const float *raw_in, const float *raw_forget,
                                    float *take, float *m_tok, int64_t stream) {
   if (n_tok <= 0 || n_seq <= 0) return 0;
   if (heads <= 0 || !raw_in || !raw_forget || !m_state || !keep || !take || !m_tok) return -2;
-  const int warps = 4, jobs = n_seq * heads;
-  mlstm_gates_kernel<<<(jobs + warps - 1) / warps, warps * 32, 0, (cudaStream_t)stream>>>(raw_in, raw_forget, raw_ld, cap, heads, m_state,
-                                                                                       cu_tok, past, slot, n_seq, keep, take, m_tok);
+  mlstm_gates_kernel<<<n_seq * heads, GATE_WARPS * 32, 0, (cudaStream_t)stream>>>(raw_in, raw_forget, raw_ld, cap, heads, m_state, cu_tok, past,
+                                                                                  slot, keep, take, m_tok);
   return launch_status();
 }
 
