@@ -270,8 +270,6 @@ static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
   const int unit = 32 / parts > N ? 32 / parts : N;               // columns per CTA: whole warps, whole 16-byte groups
   int cw = min(256 / parts, (a.dv + unit - 1) / unit * unit);
   if (cw < unit) cw = unit;
-  for (int c = cw - unit; c >= unit && c * parts >= 128; c -= unit)      // a narrower CTA when it leaves fewer idle columns in the last one
-    if ((a.dv + c - 1) / c * c < (a.dv + cw - 1) / cw * cw) cw = c;
   while (cw / 2 >= unit && (cw / 2) % unit == 0 && (cw / 2) * parts >= 64 && (int64_t)((a.dv + cw - 1) / cw) * a.heads * a.n_seq * (a.n_segs > 1 ? a.n_segs : 1) < 148) cw /= 2;   // fill the SMs
   if (cw * parts > 256 || (cw * parts) % 32) return -2;
   const int dks = parts * (RK + 4), dkr = (a.dk + N - 1) / N * N, cwr = (cw + N - 1) / N * N;

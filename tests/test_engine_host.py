@@ -5,7 +5,7 @@ import json
 import numpy as np
 import pytest
 
-from mistralrs_b200 import engine, nisasun, registry
+from mistralrs_b200 import engine, kilizen, nisasun, registry
 
 
 def test_state_slots_lowest_free_first_and_reuse():
@@ -70,7 +70,7 @@ def test_scheduler_budget_portions_and_admission():
 
 
 def test_registry_picks_by_config(tmp_path):
-    assert "Nisasun" in registry.registered() and "LlamaForCausalLM" in registry.registered()
+    assert "Nisasun" in registry.registered() and "Kilizen" in registry.registered() and "LlamaForCausalLM" in registry.registered()
     assert registry.architecture_of({"architecture": "Nisasun"}) == "Nisasun"
     assert registry.architecture_of({"architectures": ["LlamaForCausalLM"], "model_type": "llama"}) == "LlamaForCausalLM"
     (tmp_path / "config.json").write_text(json.dumps({"architecture": "Unheard"}))
@@ -100,8 +100,37 @@ def test_config_reader_shapes_and_branches():
             nisasun.NisasunConfig(c2)
 
 
+def test_kilizen_config_reader_shapes_order_and_branches():
+    cj = {"architecture": "Kilizen", "vocab": 50, "width": 24, "norm": {"eps": 1e-6}, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [
+        {"type": "attention_2", "mixer": {"heads": 4, "kv_heads": 2, "dim": 6, "vdim": 10, "scale": 0.4, "rot": {"base": 100.0, "dims": 4}}, "mlp": None},
+        {"type": "attention", "mixer": {"heads": 2, "dim": 8, "vdim": 8, "scale": 0.3, "mask": {"size": 5, "keep_first": 2}},
+         "mlp": {"kind": "moe", "expert": {"ff": 10}, "router": {"experts": 3, "top": 1}, "shared": {"ff": 7}}},
+        {"type": "mlstm", "mixer": {"heads": 3, "dim": 4, "vdim": 6, "gate_cap": 9.0}, "mlp": {"kind": "dense", "ff": 30}}]}
+    cfg = kilizen.KilizenConfig(cj)
+    assert cfg.runs() == [(0, False), (1, False), (2, False), (1, True), (2, False)]
+    sh = cfg.tensor_shapes()
+    assert "l0.norm2" not in sh and sh["l0.norm1b.alpha"] == () and sh["final.norm.b"] == (24,)
+    assert sh["l0.mix.q"] == (24, 24) and sh["l0.mix.k.b"] == (12,) and sh["l0.mix.v"] == (20, 24) and sh["l0.mix.q.norm"] == (24,) and sh["l0.mix.o"] == (24, 40)
+    assert sh["l1.mix.k"] == (16, 24) and sh["l1.mix.k.norm"] == (8,) and "l1.mix.v" not in sh and sh["l1.mix.sink"] == (2,)   # no kv_heads entry: one per head
+    assert sh["l1.mlp.e2.down"] == (24, 10) and sh["l1.mlp.shared.up"] == (7, 24) and sh["l1.mlp.router"] == (3, 24)
+    assert sh["l2.mix.i"] == (3, 24) and sh["l2.mix.f.b"] == (3,) and sh["l2.mix.norm"] == (18,) and sh["l2.mlp.up"] == (30, 24)
+    t = kilizen.random_tensors(cfg, 0)
+    assert set(t) == set(sh) and all(tuple(t[k].shape) == tuple(v) for k, v in sh.items())
+    for bad in ({"type": "other"}, {"mlp": {"kind": "sparse"}}):
+        c2 = json.loads(json.dumps(cj))
+        c2["layers"][0].update(bad)
+        with pytest.raises(NotImplementedError):
+            kilizen.KilizenConfig(c2)
+    c2 = json.loads(json.dumps(cj))
+    c2["loop"] = {"start": 2, "stop": 5, "times": 2}
+    with pytest.raises(ValueError):
+        kilizen.KilizenConfig(c2)
+
+
 def test_step_batch_layout_cpu():
     b = engine.StepBatch("cpu", [5, 6, 7, 8], [3, 1], [0, 9], [1, 0], [[2], [4, 5]], np.array([32, 33, 34, 89], dtype=np.int64), [2, 3])
     assert b.cu_tok.tolist() == [0, 3, 4] and b.seq_of_tok.tolist() == [0, 0, 0, 1] and b.pos_of_tok.tolist() == [0, 1, 2, 9]
     assert b.pages.tolist() == [[2, 0], [4, 5]] and b.slot_of_tok.tolist() == [32, 33, 34, 89] and b.rows.tolist() == [2, 3]
     assert b.past.tolist() == [0, 9] and b.slot.tolist() == [1, 0] and b.ids.tolist() == [5, 6, 7, 8]
+    many = engine.StepBatch("cpu", [0] * 76, [40, 1, 35], [0, 9, 0], [1, 0, 2], [[2, 3, 6], [4], [7, 8, 9]], np.arange(76, dtype=np.int64), [])
+    assert many.fresh == [(0, 40), (41, 35)] and many.fresh_rows.tolist() == [0, 40, 41, 35] and many.paged_tok.tolist() == [40]
