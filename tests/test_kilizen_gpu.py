@@ -3,6 +3,10 @@ then whole prompts, token-by-token decoding, portions of many sizes, mixed batch
 window and of the kept first tokens, far keys, sinks, long decoding, and greedy generation through the scheduler.
 Small random configurations made here; f32 mode is held to f32 rounding, bf16 mode to bf16 rounding."""
 import copy
+import json
+import os
+import subprocess
+import sys
 
 import numpy as np
 import pytest
@@ -87,7 +91,7 @@ def assert_close(got, want, dtype, what=""):
     if dtype == torch.float32:
         assert e.max() < TOL[dtype], (what, float(e.max()), int(e.argmax()))
     else:   # a router decision may flip under bf16 rounding of its input: a few rows may differ, none wildly
-        assert (e > TOL[dtype]).mean() <= 0.03 and np.median(e) < TOL[dtype] / 3, (what, float(e.max()), float(np.median(e)))
+        assert (e > TOL[dtype]).sum() <= max(1, 0.03 * e.size) and np.median(e) < TOL[dtype] / 3, (what, float(e.max()), float(np.median(e)))
 
 
 def replay(eng, prompts, schedule):
@@ -535,6 +539,68 @@ def test_greedy_generation_through_the_scheduler(cuda):
             if top2[0] - top2[1] > 1e-3:
                 assert int(lg.argmax()) == t
             seq.append(t)
+
+
+AWKWARD = make_cfg([attention2_layer(heads=3, kv_heads=3, dim=9, vdim=5, rot_dims=4, mlp={"kind": "dense", "ff": 51}),
+                    mlstm_layer(heads=2, dim=7, vdim=3, cap=1.5, mlp=moe(experts=3, top=2, ff=13, shared=11)),
+                    attention_layer(heads=2, kv_heads=1, dim=10, rot_dims=10, window=5, keep_first=2, mlp=moe(experts=4, top=1, ff=6, shared=0))],
+                   width=45, vocab=77, loop=(0, 3, 2))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sizes_that_align_with_nothing(cuda, dtype):
+    """Odd width, odd head sizes, odd feed-forward sizes: every kernel falls back to its unvectorised path, rows of the
+    activations start on 2-byte boundaries in bf16; the whole list of layers runs twice."""
+    model, w = build(AWKWARD, dtype, cuda, 17)
+    p = {"x": tokens(70, 77, 8), "y": tokens(33, 77, 9)}
+    eng = engine.Engine(model, max_tokens=128, max_seqs=2)
+    got = replay(eng, p, [[("x", 40), ("y", 3)], [("x", 1), ("y", 30)], [("x", 29)]])
+    for k in p:
+        assert_close(got[k], P.forward(p[k], w, AWKWARD).numpy(), dtype, k)
+
+
+def test_model_folder_through_the_command_lines(cuda, tmp_path):
+    """config.json + model.safetensors on disk -> the registry picks the class; the step-trace replay tool writes the
+    logits it is asked for (requests cut into portions, a finished request's pages reused), and the generate command
+    decodes greedily through the scheduler."""
+    from safetensors.torch import save_file
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cj = copy.deepcopy(DENSE_ONLY)
+    cj["loop"] = {"start": 0, "stop": 2, "times": 2}
+    tensors = kilizen.random_tensors(kilizen.KilizenConfig(copy.deepcopy(cj)), 41)
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(cj))
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    w = {k: v.to(F64) for k, v in tensors.items()}
+    a, b = tokens(50, 131, 1), tokens(20, 131, 2)
+    want_a, want_b = P.forward(a, w, cj).numpy(), P.forward(b, w, cj).numpy()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[30:31], "want": []}, {"id": "b", "tokens": b[:19], "want": [18]}], "end": []},
+             {"step": 2, "entries": [{"id": "b", "tokens": b[19:], "want": [0]}, {"id": "a", "tokens": a[31:], "want": [18]}], "end": ["a", "b"]},
+             {"step": 3, "entries": [{"id": "c", "tokens": b, "want": [19]}], "end": ["c"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(x) for x in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [x for x in r.stdout.split("\n") if x.startswith("done")] == ["done %d" % i for i in range(4)]
+    read = lambda i: np.fromfile(out / ("%d.f32" % i), dtype="<f4").reshape(-1, 131)
+    assert_close(read(0), want_a[[0, 29]], torch.float32)
+    assert_close(read(1), want_b[[18]], torch.float32)
+    assert_close(read(2), np.stack([want_b[19], want_a[49]]), torch.float32)
+    assert_close(read(3), want_b[[19]], torch.float32)
+    g = subprocess.run([sys.executable, os.path.join(root, "bin", "mrs-b200"), "generate", "--model", str(folder), "--dtype", "float32", "--max-new", "3",
+                        "--prompt", " ".join(map(str, b))], capture_output=True, text=True, timeout=900)
+    assert g.returncode == 0, g.stderr[-2000:]
+    gen = json.loads(g.stdout.strip().split("\n")[-1])["generated"]
+    seq = list(b)
+    for t in gen:
+        lg = torch.from_numpy(P.forward(seq, w, cj).numpy()[-1])
+        top2 = lg.topk(2).values
+        if top2[0] - top2[1] > 1e-3:
+            assert int(lg.argmax()) == t
+        seq.append(t)
+    assert len(gen) == 3
 
 
 def test_config_rejects_unknown_branches():
