@@ -237,6 +237,38 @@ def test_attention_prompt_kernels(cuda, d, kind, portions):
     close_rows(got, want, 3e-2)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("window,keep", [(0, 0), (1, 0), (40, 1), (64, 64), (65, 100), (200, 130), (17, 300)])
+def test_prompt_kernel_tile_borders(cuda, d, window, keep):
+    """The tensor-core prompt kernel alone against the plain softmax: windows and kept counts on, beside and across its
+    64-key tiles and 128-row query tiles, sequences of 33 / 128 / 129 / 400 rows at odd places of one flat batch, a sink
+    on one head only."""
+    g = torch.Generator().manual_seed(window * 7 + keep)
+    H, G, lens = 4, 2, [33, 128, 129, 400]
+    gaps = [5, 0, 3, 1]                                       # rows of other sequences between them
+    starts, at = [], 0
+    for n, gap in zip(lens, gaps):
+        at += gap
+        starts.append(at)
+        at += n
+    q = torch.randn(at, H * d, generator=g).to(torch.bfloat16)
+    k = torch.randn(at, G * d + 8, generator=g).to(torch.bfloat16)          # its own row stride
+    v = torch.randn(at, G * d, generator=g).to(torch.bfloat16)
+    sink = torch.tensor([1.5, -50.0, 0.0, -1.0])
+    out = torch.zeros(at, H * d, dtype=torch.bfloat16, device=cuda)
+    rows = torch.tensor([x for s, n in zip(starts, lens) for x in (s, n)], dtype=torch.int32, device=cuda)
+    K.prompt_attention(q.to(cuda), 0, k.to(cuda), 0, v.to(cuda), 0, rows, len(lens), max(lens), H, G, d, d ** -0.5, window, keep, sink.to(cuda), out)
+    mask = {"size": window, "keep_first": keep} if window else None
+    for s, n in zip(starts, lens):
+        want = P.sink_attention(q[s:s + n].double().view(n, H, d), k[s:s + n, :G * d].double().view(n, G, d), v[s:s + n].double().view(n, G, d),
+                                d ** -0.5, sink.double(), P.visible(n, mask))
+        close_rows(out[s:s + n].double().cpu(), want, 2e-2)
+    untouched = torch.ones(at, dtype=torch.bool)
+    for s, n in zip(starts, lens):
+        untouched[s:s + n] = False
+    assert (out.cpu()[untouched] == 0).all()
+
+
 def test_prompt_kernel_takes_several_fresh_sequences(cuda):
     """Two sequences start in one step beside a continued one: one launch covers both fresh ones, the third reads pages."""
     layer = attention_layer(heads=2, kv_heads=1, dim=64, rot_dims=16, window=40, keep_first=70, scale=0.125)
