@@ -671,6 +671,13 @@ def bench_kilizen(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
         t = timed(prefill)
         row["prefill_tok_s"], row["prefill_ms"] = prompt / t, t * 1e3
         row["prefill_ms_by_op"] = by_op(prefill)
+
+        def prefill_cut():                                   # the same prompt in two steps: the second portion continues the sequence
+            r = eng.new_request(toks)
+            eng.execute([(r, prompt // 2)])
+            eng.execute([(r, prompt - prompt // 2)])
+            eng.finish(r)
+        row["prefill_two_portions_ms"] = timed(prefill_cut) * 1e3
         row["decode"] = []
         ctx = prompt // 8
         for b in decode_batches:

@@ -138,14 +138,12 @@ int mrs_seq_window_attention(const void *q, int64_t q_ld, const void *k_cache, c
  * prepare: norm_mode 0 none, 1 per head (weights [dk], shared by the heads), 2 over the whole projection at once
  * (weights [heads * dk] and [kv_heads * dk]); then rotation of the first rot_dims entries of every q / k head in pairs
  * (i, i + rot_dims / 2) by cos_sin f32 [n_tok, rot_dims / 2, 2] (NULL: none); q and k change in place, k and v go to their
- * cache slots.  v NULL: the values are the keys as projected (before norm and rotation; needs dv == dk); v_copy, when
- * given, also receives those values ([n_tok, kv_heads, dk] with row stride v_copy_ld) for a kernel that reads fresh rows. */
+ * cache slots.  v NULL: the values are the keys as projected (before norm and rotation; needs dv == dk). */
 enum { MRS_SEQ_QK_NORM_NONE = 0, MRS_SEQ_QK_NORM_HEAD = 1, MRS_SEQ_QK_NORM_WHOLE = 2 };
 typedef struct {
   void *q, *k;
   const void *v;
-  void *v_copy;
-  int64_t q_ld, k_ld, v_ld, v_copy_ld;
+  int64_t q_ld, k_ld, v_ld;
   int dtype, norm_mode;
   const float *q_norm_w, *k_norm_w;
   float eps;
@@ -179,12 +177,14 @@ typedef struct {
   float out_scale;
 } mrs_seq_paged_attention_args;
 int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args, int64_t stream);
-/* Causal attention of sequences that START in this step over their own fresh q / k / v rows (bf16, dk = dv = d of 64 or
- * 128, rows 16-byte aligned) on tensor cores, with the same window / keep_first / sink rule.  seq_rows [n_seq][2]: the
- * first row and the row count of every such sequence inside q / k / v / out; longest = the largest row count. */
-int mrs_seq_prompt_attention(const void *q, const void *k, const void *v, void *out, const int32_t *seq_rows, int n_seq,
-                             int longest, int heads, int kv_heads, int d, int64_t q_ld, int64_t k_ld, int64_t v_ld, int64_t out_ld,
-                             float scale, int window, int keep_first, const float *sink, int64_t stream);
+/* The long portions of a step on tensor cores (bf16, dk = dv = d of 64 or 128, q / out rows 16-byte aligned), with the same
+ * window / keep_first / sink rule: queries are the portion's fresh rows of q, keys and values are read from the pages (the
+ * portion's own, stored by the preparation, and everything cached before).  portions [n][4]: first row inside q / out,
+ * row count, positions cached before the portion, row of `pages`; longest = the largest row count. */
+int mrs_seq_prompt_attention(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, void *out, int64_t out_ld,
+                             const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
+                             int page_size, int heads, int kv_heads, int d, float scale, int window, int keep_first,
+                             const float *sink, int64_t stream);
 /* x[r][c] *= scale for r < rows, c < cols (row stride ld) */
 int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream);
 

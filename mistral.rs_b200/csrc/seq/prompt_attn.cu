@@ -1,12 +1,13 @@
-// prompt_attn.cu — tensor-core attention of sequences that START in a step, over their own fresh q / k / v rows, for
-// layers whose softmax has a sink and whose window may keep the first tokens in sight.
+// prompt_attn.cu — tensor-core attention of the long portions of a step (a prompt's first portion or a later one) for
+// layers whose softmax may have a sink and whose window may keep the first tokens in sight.  Queries are the portion's
+// fresh rows; keys and values — the portion's own and everything the sequence cached before — are read from the pages,
+// where the preparation kernel has just stored them, so one kernel serves whole prompts and prompts cut anywhere.
 //
 // The tiling is the package's mma.sync prompt kernel (prefill_attn.cu): one CTA = 128 query rows of one (sequence,
-// head), 8 warps x 16 rows, Q fragments in registers, K / V tiles of 64 tokens through a double-buffered XOR-swizzled
-// shared-memory ring (cp.async), S = QK^T and O = PV as m16n8k16 MMAs with f32 accumulation, online softmax in f32 on a
-// base-2 exponent.  What differs: sequences are given as (first row, rows) pairs anywhere in the step's flat batch; k
-// and v have their own row strides (the values may live in a separate copy of the unnormed keys); the key tiles of a
-// query tile are the kept first tiles followed by the window's tiles; and the denominator ends with the sink's term.
+// head), 8 warps x 16 rows, Q fragments in registers, K / V tiles of 64 positions through a double-buffered XOR-swizzled
+// shared-memory ring (cp.async, 16 bytes at a time, the page looked up per row), S = QK^T and O = PV as m16n8k16 MMAs
+// with f32 accumulation, online softmax in f32 on a base-2 exponent.  The key tiles of a query tile are the kept first
+// tiles followed by the window's tiles; the denominator ends with the sink's term.
 #include "../mma_common.cuh"
 
 #include "../../../include/mrs_b200_seq.h"
@@ -17,11 +18,13 @@ using namespace mrs;
 constexpr int BM = 128, BN = 64, WARPS = 8, THREADS = WARPS * 32;
 
 struct Params {
-  const __nv_bfloat16 *q, *k, *v;
+  const __nv_bfloat16 *q, *k_cache, *v_cache;
   __nv_bfloat16 *o;
-  const int32_t *seq_rows;
+  const int32_t *portions;     // [n][4]: first row, rows, positions cached before (past), row of the page table
+  const int32_t *pages;
+  int pages_ld, page_size;
   int H, KVH;
-  int64_t q_ld, k_ld, v_ld, o_ld;
+  int64_t q_ld, o_ld;
   float scale_log2;
   int window, keep_first;      // window <= 0: every earlier position
   const float *sink;
@@ -37,19 +40,19 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z, h = blockIdx.y, kvh = h / (p.H / p.KVH);
-  const int seq0 = p.seq_rows[2 * b], len = p.seq_rows[2 * b + 1];
+  const int seq0 = p.portions[4 * b], len = p.portions[4 * b + 1], past = p.portions[4 * b + 2];
+  const int32_t *table = p.pages + (int64_t)p.portions[4 * b + 3] * p.pages_ld;
+  const int total = past + len;                     // positions the sequence holds after this step
   const int ntile_q = (len + BM - 1) / BM;
   const int qt = ntile_q - 1 - (int)blockIdx.x;     // heavy tiles first
   if (qt < 0) return;
-  const int q0 = qt * BM;
+  const int q0 = qt * BM;                           // row inside the portion; its position is past + row
   const T *qg = p.q + (int64_t)seq0 * p.q_ld + (int64_t)h * D;
-  const T *kg = p.k + (int64_t)seq0 * p.k_ld + (int64_t)kvh * D;
-  const T *vg = p.v + (int64_t)seq0 * p.v_ld + (int64_t)kvh * D;
   T *og = p.o + (int64_t)seq0 * p.o_ld + (int64_t)h * D;
 
-  // key tiles of this query tile: the kept first tokens that lie before the window's first tile, then the window
-  const int kv_end = min(len, q0 + BM);
-  const int win_begin = p.window > 0 ? max(0, q0 - p.window + 1) / BN * BN : 0;
+  // key tiles of this query tile: the kept first positions that lie before the window's first tile, then the window
+  const int kv_end = min(total, past + q0 + BM);
+  const int win_begin = p.window > 0 ? max(0, past + q0 - p.window + 1) / BN * BN : 0;
   const int kept_end = min(p.keep_first, win_begin);
   const int kept_tiles = (kept_end + BN - 1) / BN;                  // kept_tiles * BN <= win_begin: no key twice
   const int nt = kept_tiles + (kv_end - win_begin + BN - 1) / BN;
@@ -59,10 +62,12 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
     const int t0 = tile_start(t);
     for (int c = tid; c < BN * CPR; c += THREADS) {
       const int row = c / CPR, ch = c % CPR;
-      const bool ok = t0 + row < len;
-      const int64_t r = ok ? t0 + row : 0;
-      cp_async16(sk[buf] + tile_off<D>(row, ch), kg + r * p.k_ld + ch * 8, ok);
-      cp_async16(sv[buf] + tile_off<D>(row, ch), vg + r * p.v_ld + ch * 8, ok);
+      const int j = t0 + row;
+      const bool ok = j < kv_end;
+      const int jj = ok ? j : 0;
+      const int64_t at = (((int64_t)table[jj / p.page_size] * p.page_size + jj % p.page_size) * p.KVH + kvh) * D + ch * 8;
+      cp_async16(sk[buf] + tile_off<D>(row, ch), p.k_cache + at, ok);
+      cp_async16(sv[buf] + tile_off<D>(row, ch), p.v_cache + at, ok);
     }
     cp_async_commit();
   };
@@ -89,7 +94,7 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
 #pragma unroll
   for (int i = 0; i < DT; i++) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  const int row_a = q0 + warp * 16 + (lane >> 2);   // this thread's accumulator rows: row_a, row_a + 8
+  const int row_a = q0 + warp * 16 + (lane >> 2);   // this thread's accumulator rows (inside the portion): row_a, row_a + 8
 
   for (int t = 0; t < nt; t++) {
     const int buf = t & 1;
@@ -115,7 +120,7 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
       }
     }
 
-    const bool need_mask = p.window > 0 || t0 + BN > kv_end || t0 + BN - 1 > q0 + warp * 16;
+    const bool need_mask = p.window > 0 || t0 + BN > kv_end || t0 + BN - 1 > past + q0 + warp * 16;
     float mx[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int j = 0; j < BN / 8; j++) {
@@ -124,8 +129,8 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
         float s = sacc[j][e] * p.scale_log2;
         if (need_mask) {
           const int col = t0 + 8 * j + 2 * (lane & 3) + (e & 1);
-          const int row = row_a + ((e >> 1) << 3);
-          const bool ok = col < len && col <= row && (p.window <= 0 || row - col < p.window || col < p.keep_first);
+          const int row = past + row_a + ((e >> 1) << 3);          // the query's position
+          const bool ok = col < total && col <= row && (p.window <= 0 || row - col < p.window || col < p.keep_first);
           if (!ok) s = -INFINITY;
         }
         sacc[j][e] = s;
@@ -192,7 +197,7 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
 }
 
 template <int D>
-static int launch(const Params &p, int n_seq, int longest, cudaStream_t st) {
+static int launch(const Params &p, int n, int longest, cudaStream_t st) {
   auto kern = prompt_attention_kernel<D>;
   const size_t bytes = 4 * (size_t)BN * D * 2;
   static bool raised = false;
@@ -201,23 +206,25 @@ static int launch(const Params &p, int n_seq, int longest, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     raised = true;
   }
-  kern<<<dim3((longest + BM - 1) / BM, p.H, n_seq), THREADS, bytes, st>>>(p);
+  kern<<<dim3((longest + BM - 1) / BM, p.H, n), THREADS, bytes, st>>>(p);
   return (int)cudaGetLastError();
 }
 
 }  // namespace seqp
 
-extern "C" int mrs_seq_prompt_attention(const void *q, const void *k, const void *v, void *out, const int32_t *seq_rows, int n_seq,
-                                        int longest, int heads, int kv_heads, int d, int64_t q_ld, int64_t k_ld, int64_t v_ld, int64_t out_ld,
-                                        float scale, int window, int keep_first, const float *sink, int64_t stream) {
-  if (n_seq <= 0 || longest <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || (d != 64 && d != 128) || !seq_rows) return -2;
-  if ((q_ld | k_ld | v_ld | out_ld) % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)) return -3;
+extern "C" int mrs_seq_prompt_attention(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, void *out, int64_t out_ld,
+                                        const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
+                                        int page_size, int heads, int kv_heads, int d, float scale, int window, int keep_first,
+                                        const float *sink, int64_t stream) {
+  if (n_portions <= 0 || longest <= 0) return 0;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || (d != 64 && d != 128) || !portions || !pages || page_size <= 0) return -2;
+  if ((q_ld | out_ld) % 8 || (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)) return -3;
   seqp::Params p = {};
-  p.q = (const __nv_bfloat16 *)q; p.k = (const __nv_bfloat16 *)k; p.v = (const __nv_bfloat16 *)v; p.o = (__nv_bfloat16 *)out;
-  p.seq_rows = seq_rows; p.H = heads; p.KVH = kv_heads;
-  p.q_ld = q_ld; p.k_ld = k_ld; p.v_ld = v_ld; p.o_ld = out_ld;
+  p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
+  p.o = (__nv_bfloat16 *)out;
+  p.portions = portions; p.pages = pages; p.pages_ld = pages_ld; p.page_size = page_size;
+  p.H = heads; p.KVH = kv_heads; p.q_ld = q_ld; p.o_ld = out_ld;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.keep_first = keep_first > 0 ? keep_first : 0; p.sink = sink;
-  return d == 128 ? seqp::launch<128>(p, n_seq, longest, (cudaStream_t)stream) : seqp::launch<64>(p, n_seq, longest, (cudaStream_t)stream);
+  return d == 128 ? seqp::launch<128>(p, n_portions, longest, (cudaStream_t)stream) : seqp::launch<64>(p, n_portions, longest, (cudaStream_t)stream);
 }

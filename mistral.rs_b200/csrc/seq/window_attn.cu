@@ -54,12 +54,9 @@ __global__ void attention_prepare_kernel(const mrs_seq_attn_prepare_args a) {
       const bool normed = a.norm_mode != MRS_SEQ_QK_NORM_NONE;
       T *cached = (!is_q && slot >= 0) ? (T *)a.k_cache + (slot * kv_heads + hh) * dk : nullptr;
       if (!is_q && a.v == nullptr) {      // the values are the keys as projected
-        T *vc = slot >= 0 ? (T *)a.v_cache + (slot * kv_heads + hh) * dv : nullptr;
-        T *cp = a.v_copy ? (T *)a.v_copy + (int64_t)t * a.v_copy_ld + hh * dk : nullptr;
-        for (int d = lane; d < dk; d += 32) {
-          const T raw = src[d];
-          if (vc) vc[d] = raw;
-          if (cp) cp[d] = raw;
+        if (slot >= 0) {
+          T *vc = (T *)a.v_cache + (slot * kv_heads + hh) * dv;
+          for (int d = lane; d < dk; d += 32) vc[d] = src[d];
         }
         __syncwarp();
       }

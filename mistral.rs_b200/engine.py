@@ -80,7 +80,7 @@ class StateSlots:
 class StepBatch:
     """Device-side integer description of one step.  Built on the host into one pinned buffer, copied once."""
 
-    FRESH_MIN = 32     # a sequence that starts with at least this many tokens may take the prompt-attention kernels
+    FRESH_MIN = 32     # a portion of at least this many tokens may take the prompt-attention kernels
 
     def __init__(self, device, ids, counts, pasts, slots, tables, slot_of_tok, rows, pages_ld=None):
         self.device, self._pages_ld = device, pages_ld
@@ -101,9 +101,13 @@ class StepBatch:
         is_fresh = [p == 0 and c >= self.FRESH_MIN for p, c in zip(pasts, counts)]
         self.fresh = [(int(cu[b]), int(counts[b])) for b in range(n_seq) if is_fresh[b]]      # (first row, rows) per such sequence
         paged = np.concatenate([np.arange(cu[b], cu[b + 1], dtype=np.int32) for b in range(n_seq) if not is_fresh[b]] + [np.zeros(0, np.int32)])
-        fresh_rows = np.asarray(self.fresh, dtype=np.int32).reshape(-1)                        # (first row, rows) pairs for the kernels
+        # long portions, fresh or continued: (first row, rows, tokens cached before, sequence) for kernels that tile a portion's rows
+        is_long = [c >= self.FRESH_MIN for c in counts]
+        self.long = [(int(cu[b]), int(counts[b]), int(pasts[b]), b) for b in range(n_seq) if is_long[b]]
+        long_rows = np.asarray(self.long, dtype=np.int32).reshape(-1)
+        short = np.concatenate([np.arange(cu[b], cu[b + 1], dtype=np.int32) for b in range(n_seq) if not is_long[b]] + [np.zeros(0, np.int32)])
         parts = [np.asarray(ids, dtype=np.int32), cu, np.asarray(pasts, dtype=np.int32), np.asarray(slots, dtype=np.int32), seq_of, pos_of,
-                 pages.reshape(-1), np.asarray(rows, dtype=np.int32), paged, fresh_rows]
+                 pages.reshape(-1), np.asarray(rows, dtype=np.int32), paged, long_rows, short]
         sizes = [p.size for p in parts]
         pad = sum(sizes) % 2                                       # keep the int64 tail 8-byte aligned
         total = sum(sizes) + pad + 2 * n_tok
@@ -128,7 +132,8 @@ class StepBatch:
         self.pages = cut(6).view(n_seq, pages_ld)
         self.rows = cut(7)
         self.paged_tok = cut(8)                                    # tokens of the sequences not in `fresh`
-        self.fresh_rows = cut(9)
+        self.long_rows = cut(9)                                    # 4 integers per entry of `long`
+        self.short_tok = cut(10)                                   # tokens of the sequences not in `long`
         at = int(o[-1]) + pad
         self.slot_of_tok = dev[at:at + 2 * n_tok].view(torch.int64)
 

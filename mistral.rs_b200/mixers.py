@@ -115,33 +115,31 @@ class WindowAttention:
 
     def attend(self, y, col0, batch, cache, page_size, out, out_col=0, out_scale=1.0):
         """y holds q | k | v (q | k when the values are the keys) from column col0; writes heads * dv columns of `out`
-        from out_col.  Keys and values of the new tokens are normed, rotated and stored first.  A sequence that starts
-        in this step with a long enough portion (batch.fresh) runs on tensor-core prompt kernels over its fresh q / k / v
-        when they fit (bf16, equal head sizes of 64 or 128, 16-byte aligned rows); every other token — portions that
-        continue a sequence, decoded tokens, other head sizes, f32 — reads its keys from the pages."""
+        from out_col.  Keys and values of the new tokens are normed, rotated and stored first.  Long portions (32 tokens
+        or more) run on tensor cores when they fit (bf16, equal head sizes of 64 or 128, 16-byte aligned rows): when every
+        one of them starts its sequence and the layer has neither sink nor kept first tokens, on the package's prompt
+        kernels over the fresh q / k / v; otherwise — sinks, kept tokens, portions that continue a sequence — on the
+        sequence library's prompt kernel, which reads keys and values from the pages.  Every other token (short portions,
+        decoded tokens, other head sizes, f32) runs on the (token, head) kernel over the pages."""
         kc = col0 + self.heads * self.dk
         vc = None if self.values_from_keys else kc + self.kv_heads * self.dk
-        aligned = all(v % 8 == 0 for v in (y.stride(0), col0, out.stride(0), out_col))
-        fresh = bool(batch.fresh) and y.dtype == torch.bfloat16 and self.dk == self.dv and self.dk in (64, 128) and aligned
-        plain = self.sink is None and self.keep_first == 0           # the package's prompt kernels know neither
-        v_copy = torch.empty(y.shape[0], self.kv_heads * self.dk, dtype=y.dtype, device=y.device) if fresh and vc is None else None
         cos_sin = self.rotation.table(batch) if self.rotation is not None else None
         K.attention_prepare(y, col0, kc, vc, self.norm_mode, self.q_norm_w, self.k_norm_w, self.eps, self.heads, self.kv_heads, self.dk,
-                            self.dv, cache["k"], cache["v"], batch.slot_of_tok, cos_sin, self.rotation.dims if cos_sin is not None else 0,
-                            v_copy)
+                            self.dv, cache["k"], cache["v"], batch.slot_of_tok, cos_sin, self.rotation.dims if cos_sin is not None else 0)
         tok_index = None
-        if fresh:
-            vt, vcol = (y, vc) if v_copy is None else (v_copy, 0)
-            if plain and v_copy is None:
+        aligned = all(v % 8 == 0 for v in (y.stride(0), col0, out.stride(0), out_col))
+        if batch.long and y.dtype == torch.bfloat16 and self.dk == self.dv and self.dk in (64, 128) and aligned:
+            plain = self.sink is None and self.keep_first == 0 and vc is not None       # what the package's prompt kernels know
+            if plain and len(batch.fresh) == len(batch.long):
                 for row0, rows in batch.fresh:
                     K.fresh_prompt_attention(y, row0, rows, col0, kc, vc, self.heads, self.kv_heads, self.dk, self.scale, self.window, out, out_col)
             else:
-                K.prompt_attention(y, col0, y, kc, vt, vcol, batch.fresh_rows, len(batch.fresh), max(r for _, r in batch.fresh), self.heads,
-                                   self.kv_heads, self.dk, self.scale, self.window, self.keep_first, self.sink, out, out_col)
+                K.prompt_attention(y, col0, cache["k"], cache["v"], batch, page_size, self.heads, self.kv_heads, self.dk, self.scale, self.window,
+                                   self.keep_first, self.sink, out, out_col)
             if out_scale != 1.0:
-                for row0, rows in batch.fresh:
+                for row0, rows, _, _ in batch.long:
                     K.scale_rows(out, row0, rows, out_col, self.heads * self.dv, out_scale)
-            tok_index = batch.paged_tok
+            tok_index = batch.short_tok
             if tok_index.numel() == 0:
                 return
         K.paged_attention(y, col0, cache["k"], cache["v"], self.heads, self.kv_heads, self.dk, self.dv, self.scale, self.window,

@@ -54,8 +54,8 @@ class ScanArgs(ctypes.Structure):
                 ("seg_state", ctypes.c_void_p), ("seg_decay", ctypes.c_void_p), ("seg_len", ctypes.c_int), ("n_segs", ctypes.c_int)]
 
 class AttnPrepareArgs(ctypes.Structure):
-    _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("v_copy", ctypes.c_void_p),
-                ("q_ld", ctypes.c_int64), ("k_ld", ctypes.c_int64), ("v_ld", ctypes.c_int64), ("v_copy_ld", ctypes.c_int64),
+    _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("q_ld", ctypes.c_int64), ("k_ld", ctypes.c_int64), ("v_ld", ctypes.c_int64),
                 ("dtype", ctypes.c_int), ("norm_mode", ctypes.c_int),
                 ("q_norm_w", ctypes.c_void_p), ("k_norm_w", ctypes.c_void_p), ("eps", ctypes.c_float),
                 ("heads", ctypes.c_int), ("kv_heads", ctypes.c_int), ("dk", ctypes.c_int), ("dv", ctypes.c_int),
@@ -314,16 +314,13 @@ def rotation_table(pos_of_tok, freq, mag):
 
 
 def attention_prepare(y, q_col, k_col, v_col, norm_mode, q_norm_w, k_norm_w, eps, heads, kv_heads, dk, dv, k_cache, v_cache, slot_of_tok,
-                      cos_sin=None, rot_dims=0, v_copy=None):
-    """q | k | v are column ranges of y.  v_col None: the values are the keys as projected; v_copy [T, kv_heads * dk], when
-    given, also receives them."""
+                      cos_sin=None, rot_dims=0):
+    """q | k | v are column ranges of y.  v_col None: the values are the keys as projected."""
     a = AttnPrepareArgs()
     ld = y.stride(0)
     a.q, a.k, a.q_ld, a.k_ld = _p(y, q_col).value, _p(y, k_col).value, ld, ld
     if v_col is not None:
         a.v, a.v_ld = _p(y, v_col).value, ld
-    elif v_copy is not None:
-        a.v_copy, a.v_copy_ld = v_copy.data_ptr(), v_copy.stride(0)
     a.dtype, a.norm_mode = DTYPE_CODE[y.dtype], norm_mode
     a.q_norm_w, a.k_norm_w, a.eps = _p(q_norm_w).value, _p(k_norm_w).value, eps
     a.heads, a.kv_heads, a.dk, a.dv = heads, kv_heads, dk, dv
@@ -347,13 +344,13 @@ def paged_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, 
     _ok(lib().mrs_seq_paged_attention(ctypes.byref(a), _st(y)), "paged_attention")
 
 
-def prompt_attention(q, q_col, k, k_col, v, v_col, seq_rows, n_seq, longest, heads, kv_heads, d, scale, window, keep_first, sink, out,
-                     out_col=0):
-    """Sequences that start in this step, over their own fresh rows (bf16, head size 64 or 128) on tensor cores.
-    seq_rows i32 [n_seq, 2]: first row and row count of every such sequence; q / k / v: column ranges of 2-D tensors."""
-    _ok(lib().mrs_seq_prompt_attention(_p(q, q_col), _p(k, k_col), _p(v, v_col), _p(out, out_col), _p(seq_rows), _i(n_seq), _i(longest),
-                                       _i(heads), _i(kv_heads), _i(d), _l(q.stride(0)), _l(k.stride(0)), _l(v.stride(0)), _l(out.stride(0)),
-                                       _f(scale), _i(int(window)), _i(int(keep_first)), _p(sink), _st(q)), "prompt_attention")
+def prompt_attention(y, q_col, k_cache, v_cache, batch, page_size, heads, kv_heads, d, scale, window, keep_first, sink, out, out_col=0):
+    """The long portions of the step (batch.long: fresh or continued) on tensor cores: queries from their rows of y, keys
+    and values from the pages (bf16, head size 64 or 128)."""
+    _ok(lib().mrs_seq_prompt_attention(_p(y, q_col), _l(y.stride(0)), _p(k_cache), _p(v_cache), _p(out, out_col), _l(out.stride(0)),
+                                       _p(batch.long_rows), _i(len(batch.long)), _i(max(n for _, n, _, _ in batch.long)), _p(batch.pages),
+                                       _i(batch.pages.shape[1]), _i(page_size), _i(heads), _i(kv_heads), _i(d), _f(scale), _i(int(window)),
+                                       _i(int(keep_first)), _p(sink), _st(y)), "prompt_attention")
 
 
 # ---- stabilised matrix memory ---------------------------------------------------------------------------

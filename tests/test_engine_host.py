@@ -133,4 +133,7 @@ def test_step_batch_layout_cpu():
     assert b.pages.tolist() == [[2, 0], [4, 5]] and b.slot_of_tok.tolist() == [32, 33, 34, 89] and b.rows.tolist() == [2, 3]
     assert b.past.tolist() == [0, 9] and b.slot.tolist() == [1, 0] and b.ids.tolist() == [5, 6, 7, 8]
     many = engine.StepBatch("cpu", [0] * 76, [40, 1, 35], [0, 9, 0], [1, 0, 2], [[2, 3, 6], [4], [7, 8, 9]], np.arange(76, dtype=np.int64), [])
-    assert many.fresh == [(0, 40), (41, 35)] and many.fresh_rows.tolist() == [0, 40, 41, 35] and many.paged_tok.tolist() == [40]
+    assert many.fresh == [(0, 40), (41, 35)] and many.paged_tok.tolist() == [40]
+    assert many.long == [(0, 40, 0, 0), (41, 35, 0, 2)] and many.long_rows.tolist() == [0, 40, 0, 0, 41, 35, 0, 2] and many.short_tok.tolist() == [40]
+    cont = engine.StepBatch("cpu", [0] * 36, [33, 3], [20, 0], [1, 0], [[2, 3, 6, 7], [4]], np.arange(36, dtype=np.int64), [])
+    assert cont.fresh == [] and cont.long == [(0, 33, 20, 0)] and cont.short_tok.tolist() == [33, 34, 35] and cont.paged_tok.numel() == 36

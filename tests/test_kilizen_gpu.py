@@ -226,9 +226,9 @@ def test_attention_other_sizes(cuda, layer):
 @pytest.mark.parametrize("kind", ["attention", "attention_2"])
 @pytest.mark.parametrize("portions", [[300], [70, 1, 200, 29], [3, 297]])
 def test_attention_prompt_kernels(cuda, d, kind, portions):
-    """bf16 with equal head sizes of 64 / 128: a sequence's first portion of 32 tokens or more runs on the tensor-core
-    prompt kernel over the fresh q / k / v (sink, window and kept first tokens included; with values that are the keys
-    it reads them from a copy of the unnormed keys); the pages must still be filled for what follows."""
+    """bf16 with equal head sizes of 64 / 128: portions of 32 tokens or more, first or later, run on the tensor-core
+    prompt kernel (sink, window and kept first tokens included), which reads keys and values — with values that are the
+    keys: the unnormed keys — from the pages; single tokens in between take the (token, head) kernel."""
     if kind == "attention":
         layer = attention_layer(heads=4, kv_heads=2, dim=d, rot_dims=32, window=40, keep_first=5, scale=d ** -0.5)   # later query tiles: kept tile + window tiles
     else:
@@ -241,36 +241,46 @@ def test_attention_prompt_kernels(cuda, d, kind, portions):
 @pytest.mark.parametrize("window,keep", [(0, 0), (1, 0), (40, 1), (64, 64), (65, 100), (200, 130), (17, 300)])
 def test_prompt_kernel_tile_borders(cuda, d, window, keep):
     """The tensor-core prompt kernel alone against the plain softmax: windows and kept counts on, beside and across its
-    64-key tiles and 128-row query tiles, sequences of 33 / 128 / 129 / 400 rows at odd places of one flat batch, a sink
-    on one head only."""
+    64-key tiles and 128-row query tiles; portions of 33 / 128 / 129 / 400 rows in one flat batch, two of which continue a
+    sequence whose earlier keys are only in the pages (70 and 130 of them, neither a multiple of a tile or a page); a
+    sink on one head only; rows of short portions in between stay untouched."""
     g = torch.Generator().manual_seed(window * 7 + keep)
-    H, G, lens = 4, 2, [33, 128, 129, 400]
-    gaps = [5, 0, 3, 1]                                       # rows of other sequences between them
-    starts, at = [], 0
-    for n, gap in zip(lens, gaps):
-        at += gap
-        starts.append(at)
-        at += n
-    q = torch.randn(at, H * d, generator=g).to(torch.bfloat16)
-    k = torch.randn(at, G * d + 8, generator=g).to(torch.bfloat16)          # its own row stride
-    v = torch.randn(at, G * d, generator=g).to(torch.bfloat16)
+    H, G, page = 4, 2, 16
+    seqs = [(33, 0), (128, 70), (3, 9), (129, 0), (400, 130)]            # (new rows, cached before)
+    portions, first_page = [], 1
+    for i, (n, past) in enumerate(seqs):
+        portions.append((n, past, i, first_page))
+        first_page += -(-(past + n) // page)
+    batch = seq_batch(cuda, portions, page_size=page)
+    assert [x[1] for x in batch.long] == [33, 128, 129, 400]
+    n_rows = sum(n for n, _ in seqs)
+    q = torch.randn(n_rows, H * d + 8, generator=g).to(torch.bfloat16)      # a row stride of its own
+    k_cache = torch.zeros(first_page * page, G, d, dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    ks, vs = [], []
+    for n, past, _, fp in portions:
+        kk, vv = torch.randn(past + n, G, d, generator=g).to(torch.bfloat16), torch.randn(past + n, G, d, generator=g).to(torch.bfloat16)
+        k_cache[fp * page:fp * page + past + n], v_cache[fp * page:fp * page + past + n] = kk, vv      # its pages are consecutive here
+        ks.append(kk), vs.append(vv)
     sink = torch.tensor([1.5, -50.0, 0.0, -1.0])
-    out = torch.zeros(at, H * d, dtype=torch.bfloat16, device=cuda)
-    rows = torch.tensor([x for s, n in zip(starts, lens) for x in (s, n)], dtype=torch.int32, device=cuda)
-    K.prompt_attention(q.to(cuda), 0, k.to(cuda), 0, v.to(cuda), 0, rows, len(lens), max(lens), H, G, d, d ** -0.5, window, keep, sink.to(cuda), out)
+    out = torch.zeros(n_rows, H * d, dtype=torch.bfloat16, device=cuda)
+    K.prompt_attention(q.to(cuda), 0, k_cache.to(cuda), v_cache.to(cuda), batch, page, H, G, d, d ** -0.5, window, keep, sink.to(cuda), out)
     mask = {"size": window, "keep_first": keep} if window else None
-    for s, n in zip(starts, lens):
-        want = P.sink_attention(q[s:s + n].double().view(n, H, d), k[s:s + n, :G * d].double().view(n, G, d), v[s:s + n].double().view(n, G, d),
-                                d ** -0.5, sink.double(), P.visible(n, mask))
-        close_rows(out[s:s + n].double().cpu(), want, 2e-2)
-    untouched = torch.ones(at, dtype=torch.bool)
-    for s, n in zip(starts, lens):
-        untouched[s:s + n] = False
-    assert (out.cpu()[untouched] == 0).all()
+    row0 = 0
+    for (n, past), kk, vv in zip(seqs, ks, vs):
+        got = out[row0:row0 + n].double().cpu()
+        if n < 32:
+            assert (got == 0).all()
+        else:
+            qq = torch.zeros(past + n, H, d, dtype=F64)
+            qq[past:] = q[row0:row0 + n, :H * d].double().view(n, H, d)
+            want = P.sink_attention(qq, kk.double(), vv.double(), d ** -0.5, sink.double(), P.visible(past + n, mask))[past:]
+            close_rows(got, want, 2e-2)
+        row0 += n
 
 
-def test_prompt_kernel_takes_several_fresh_sequences(cuda):
-    """Two sequences start in one step beside a continued one: one launch covers both fresh ones, the third reads pages."""
+def test_prompt_kernel_takes_several_sequences(cuda):
+    """Two sequences start in one step beside a long portion that continues a third: one launch covers all three."""
     layer = attention_layer(heads=2, kv_heads=1, dim=64, rot_dims=16, window=40, keep_first=70, scale=0.125)
     cj = make_cfg([layer], width=64)
     model, w = build(cj, torch.bfloat16, cuda, 7)
@@ -280,7 +290,7 @@ def test_prompt_kernel_takes_several_fresh_sequences(cuda):
     hs = [torch.randn(n, 64, generator=g).to(torch.bfloat16) for n in (150, 33, 60)]
     mixer.forward(hs[2][:20].to(cuda).contiguous(), seq_batch(cuda, [(20, 0, 2, 30)]), cache)
     b = seq_batch(cuda, [(150, 0, 0, 1), (40, 20, 2, 30), (33, 0, 1, 12)])
-    assert len(b.fresh) == 2
+    assert len(b.fresh) == 2 and len(b.long) == 3
     got = mixer.forward(torch.cat([hs[0], hs[2][20:], hs[1]]).to(cuda).contiguous(), b, cache).double().cpu()
     want = [plain_mixer(layer, h.double(), w, 1e-5) for h in hs]
     close_rows(got, torch.cat([want[0], want[2][20:], want[1]]), 3e-2)
