@@ -313,15 +313,19 @@ class RoutedExperts:
             counts, order = K.moe_sort(experts, self.n_experts)
             xs = K.moe_gather(h, order, self.top)
             ys = torch.empty_like(xs)
-            at = 0
+            spans, at = [], 0
             for e, n in enumerate(counts.tolist()):
                 if n:
-                    hid = linear(xs[at:at + n], self.w_gate_up[e])
-                    if self.gated:
-                        hid = K.glu_split(hid, self.act)
-                    else:
-                        K.activate_cols(hid, 0, hid.shape[1], self.act)
-                    torch.mm(hid, self.w_down[e].t(), out=ys[at:at + n])
+                    spans.append((e, at, at + n))
                     at += n
+            hid = torch.empty(xs.shape[0], self.w_gate_up.shape[1], dtype=xs.dtype, device=xs.device)
+            for e, a, b in spans:
+                torch.mm(xs[a:b], self.w_gate_up[e].t(), out=hid[a:b])
+            if self.gated:                                   # one activation pass over all experts' rows
+                hid = K.glu_split(hid, self.act)
+            else:
+                K.activate_cols(hid, 0, hid.shape[1], self.act)
+            for e, a, b in spans:
+                torch.mm(hid[a:b], self.w_down[e].t(), out=ys[a:b])
             out = K.moe_combine(ys, order, weights)
         return out if self.shared is None else self.shared.forward_added_to(h, out)
