@@ -589,10 +589,10 @@ def bench_nisasun(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
 def kilizen_bench_config(width, vocab=32000):
     """Four layers, one of each kind of mixer and feed-forward, at sizes of a real model's layers of this width."""
     H = width // 128
-    rot = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
     win = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot, "mask": {"size": 1024, "keep_first": 64}}
-    full = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 128}}
-    mem = {"heads": H, "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    full = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 128}}
+    mem = {"heads": H, "dim": 128, "vdim": 128, "gate_cap": 10.0}
     dense = {"kind": "dense", "ff": 4 * width}
     moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 16, "top": 2}, "shared": {"ff": width}}
     return {"architecture": "Kilizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
